@@ -1,0 +1,191 @@
+// Mixing over time channel by channel: what a sequence keeps is a vector, one number (or a few) per channel.
+//
+//   residual_conv   out_t = x_t + sum_j w[c, j] x_(t - taps + 1 + j)   a short causal convolution per channel, added to
+//                   its own input; zeros before the sequence's start; the last taps - 1 inputs are the sequence's state
+//   conv_keep       the last taps - 1 inputs of every sequence, kept for the next step
+//   min_gru         S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, z = sigmoid(a), c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0);
+//                   out_t = S_t * silu(g_t).  a, u, g are the 32-bit sums of the projections; S is 32-bit and carried on.
+//
+// All arithmetic is 32-bit.  The recurrence is linear in S, so a sequence's rows of a step are cut into chunks that
+// are walked side by side: each chunk first as a map S -> A S + B, then, from the state the chunks before it leave,
+// once more for the outputs.  One row is one chunk: a plain update.
+#include "common.cuh"
+
+using namespace kvad;
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// A block per (row, chunk of 512 channels).  Inputs before the step's first row of the sequence come from the kept
+// inputs [taps - 1, channels] (the oldest first), inputs before position 0 are zero.  `shift`: every sequence brings
+// one row, so the thread that owns (row, channel) also moves the kept inputs on by one - no other block reads them.
+template <typename T>
+__global__ void __launch_bounds__(128)
+residual_conv_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ taps, T* __restrict__ out, int64_t ld_out,
+                     float* __restrict__ state, int64_t state_stride, int64_t state_off, const int* __restrict__ row_seq,
+                     const int* __restrict__ row_pos, const int* __restrict__ seq_starts, const int* __restrict__ seq_slots,
+                     int channels, int n_taps, int shift) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, s = row_seq[r], pos = row_pos[r], first = seq_starts[s];
+  const int p0 = pos - (r - first), keep = n_taps - 1;
+  float* kept = state + (int64_t)seq_slots[s] * state_stride + state_off;
+  const int lo = blockIdx.y * 512, hi = min(lo + 512, channels);
+#pragma unroll 2
+  for (int c = lo + threadIdx.x; c < hi; c += 128) {
+    const float own = to_f32(x[(int64_t)r * ld_x + c]);
+    float acc = 0.f, old[15];
+    for (int j = 0; j < keep; ++j) {
+      const int pp = pos - keep + j;
+      float xv = 0.f;
+      if (pp >= p0) xv = to_f32(x[(int64_t)(first + pp - p0) * ld_x + c]);
+      else if (pp >= 0) xv = kept[(int64_t)(pp - p0 + keep) * channels + c];
+      if (j < 15) old[j] = xv;
+      acc = fmaf(to_f32(taps[(int64_t)c * n_taps + j]), xv, acc);
+    }
+    acc = fmaf(to_f32(taps[(int64_t)c * n_taps + keep]), own, acc);
+    out[(int64_t)r * ld_out + c] = from_f32<T>(own + acc);
+    if (shift) {
+      for (int j = 0; j + 1 < keep; ++j) kept[(int64_t)j * channels + c] = old[j + 1];
+      if (keep > 0) kept[(int64_t)(keep - 1) * channels + c] = own;
+    }
+  }
+}
+
+// A thread per (sequence, channel): the inputs at the sequence's last taps - 1 positions, from this step's rows or,
+// where the step brought fewer, from what was kept before.
+template <typename T>
+__global__ void conv_keep_kernel(const T* __restrict__ x, int64_t ld_x, float* __restrict__ state, int64_t state_stride,
+                                 int64_t state_off, const int* __restrict__ seq_starts, const int* __restrict__ seq_slots,
+                                 int n_seqs, int channels, int n_taps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n_seqs * channels) return;
+  const int s = (int)(i / channels), c = (int)(i - (int64_t)s * channels);
+  const int first = seq_starts[s], n_new = seq_starts[s + 1] - first, keep = n_taps - 1;
+  float* kept = state + (int64_t)seq_slots[s] * state_stride + state_off;
+  float old[15];
+  for (int j = 0; j < keep; ++j) old[j] = kept[(int64_t)j * channels + c];
+  for (int j = 0; j < keep; ++j) {
+    const int from_new = n_new - keep + j;          // index among this step's rows, if not negative
+    kept[(int64_t)j * channels + c] = from_new >= 0 ? to_f32(x[(int64_t)(first + from_new) * ld_x + c]) : old[j + n_new];
+  }
+}
+
+__device__ __forceinline__ void gru_terms(float a, float u, float& z, float& cand) {
+  z = sigmoid_f(a);
+  cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+}
+
+// Block (32 channels, n_chunks chunks) per (32 channels, sequence).  zug: [rows, ld] with the three projections at
+// columns off_z, off_u, off_g.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+min_gru_kernel(const float* __restrict__ zug, int64_t ld, int off_z, int off_u, int off_g, T* __restrict__ out, int64_t ld_out,
+               float* __restrict__ state, int64_t state_stride, int64_t state_off, const int* __restrict__ seq_starts,
+               const int* __restrict__ seq_slots, int width) {
+  extern __shared__ float sm[];            // A [chunks][32], B [chunks][32]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.y, c = blockIdx.x * 32 + threadIdx.x, j = threadIdx.y, n_chunks = blockDim.y;
+  const int first = seq_starts[s], n_new = seq_starts[s + 1] - first;
+  const int per = (n_new + n_chunks - 1) / n_chunks;
+  const int lo = min(j * per, n_new), hi = min(lo + per, n_new);
+  const bool live = c < width;
+  float* A = sm;
+  float* B = sm + n_chunks * 32;
+  if (n_chunks > 1) {
+    float a_run = 1.f, b_run = 0.f;
+    if (live) {
+#pragma unroll 4
+      for (int t = lo; t < hi; ++t) {
+        const float* row = zug + (int64_t)(first + t) * ld;
+        float z, cand;
+        gru_terms(row[off_z + c], row[off_u + c], z, cand);
+        a_run *= 1.f - z;
+        b_run = fmaf(z, cand, (1.f - z) * b_run);
+      }
+    }
+    A[j * 32 + threadIdx.x] = a_run;
+    B[j * 32 + threadIdx.x] = b_run;
+    __syncthreads();
+  }
+  if (!live) return;
+  float* kept = state + (int64_t)seq_slots[s] * state_stride + state_off + c;
+  float S = *kept;
+  for (int i = 0; i < j; ++i) S = fmaf(A[i * 32 + threadIdx.x], S, B[i * 32 + threadIdx.x]);
+#pragma unroll 4
+  for (int t = lo; t < hi; ++t) {
+    const float* row = zug + (int64_t)(first + t) * ld;
+    float z, cand;
+    gru_terms(row[off_z + c], row[off_u + c], z, cand);
+    S = fmaf(z, cand, (1.f - z) * S);
+    out[(int64_t)(first + t) * ld_out + c] = from_f32<T>(S * silu_f(row[off_g + c]));
+  }
+  if (hi == n_new && (lo < hi || j == 0)) *kept = S;       // the chunk that holds the last row (an empty step: nothing changes)
+}
+
+}  // namespace
+
+KVAD_EXPORT int kvad_residual_conv(int dtype, const void* x, int64_t ld_x, const void* taps, void* out, int64_t ld_out, float* state,
+                                   int64_t state_stride, int64_t state_off, const int* row_seq, const int* row_pos, const int* seq_starts,
+                                   const int* seq_slots, int n_rows, int channels, int n_taps, int shift, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && channels > 0 && n_taps >= 1 && n_taps <= 16, "residual_conv: 1 to 16 taps, got %d", n_taps);
+  KVAD_REQUIRE(x && taps && out && state && ld_x >= channels && ld_out >= channels, "residual_conv: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(n_rows, (channels + 511) / 512), block(128);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(residual_conv_kernel<float>, grid, block, 0, stream, (const float*)x, ld_x, (const float*)taps, (float*)out, ld_out, state,
+                state_stride, state_off, row_seq, row_pos, seq_starts, seq_slots, channels, n_taps, shift);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(residual_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ld_x, (const __nv_bfloat16*)taps,
+                (__nv_bfloat16*)out, ld_out, state, state_stride, state_off, row_seq, row_pos, seq_starts, seq_slots, channels, n_taps, shift);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "residual_conv: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("residual_conv");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_conv_keep(int dtype, const void* x, int64_t ld_x, float* state, int64_t state_stride, int64_t state_off,
+                               const int* seq_starts, const int* seq_slots, int n_seqs, int channels, int n_taps, cudaStream_t stream) {
+  KVAD_REQUIRE(n_seqs >= 0 && channels > 0 && n_taps >= 1 && n_taps <= 16, "conv_keep: bad sizes");
+  if (n_seqs == 0 || n_taps == 1) return KVAD_OK;
+  const int64_t total = (int64_t)n_seqs * channels;
+  dim3 grid((unsigned)((total + 127) / 128)), block(128);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(conv_keep_kernel<float>, grid, block, 0, stream, (const float*)x, ld_x, state, state_stride, state_off, seq_starts, seq_slots,
+                n_seqs, channels, n_taps);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(conv_keep_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ld_x, state, state_stride, state_off,
+                seq_starts, seq_slots, n_seqs, channels, n_taps);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "conv_keep: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("conv_keep");
+  return KVAD_OK;
+}
+
+// n_chunks: into how many chunks a sequence's rows of the step are cut (1..32; the caller chooses by the step's shape).
+KVAD_EXPORT int kvad_min_gru(int out_dtype, const float* zug, int64_t ld, int off_z, int off_u, int off_g, void* out, int64_t ld_out,
+                             float* state, int64_t state_stride, int64_t state_off, const int* seq_starts, const int* seq_slots,
+                             int n_seqs, int width, int n_chunks, cudaStream_t stream) {
+  KVAD_REQUIRE(n_seqs >= 0 && width > 0 && n_chunks >= 1 && n_chunks <= 32 && zug && out && state, "min_gru: bad arguments");
+  KVAD_REQUIRE(ld >= width && ld_out >= width && state_stride >= state_off + width, "min_gru: rows or state shorter than the width");
+  if (n_seqs == 0) return KVAD_OK;
+  dim3 grid((width + 31) / 32, n_seqs), block(32, n_chunks);
+  const size_t smem = (size_t)2 * 32 * n_chunks * sizeof(float);
+  if (out_dtype == KVAD_DTYPE_F32)
+    kvad_launch(min_gru_kernel<float>, grid, block, smem, stream, zug, ld, off_z, off_u, off_g, (float*)out, ld_out, state, state_stride,
+                state_off, seq_starts, seq_slots, width);
+  else if (out_dtype == KVAD_DTYPE_BF16)
+    kvad_launch(min_gru_kernel<__nv_bfloat16>, grid, block, smem, stream, zug, ld, off_z, off_u, off_g, (__nv_bfloat16*)out, ld_out, state,
+                state_stride, state_off, seq_starts, seq_slots, width);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "min_gru: unknown dtype %d", out_dtype);
+  KVAD_CHECK_LAUNCH("min_gru");
+  return KVAD_OK;
+}
+
+KVAD_DEFINE_LAST_ERROR()

@@ -1,7 +1,11 @@
 // A routed feed-forward: every row picks `top` of E experts, each a small gated feed-forward of its own.
 //
 //   moe_route        z = router logits (32-bit) -> the `top` largest (ties: the lower index), weights = softmax over
-//                    the chosen logits only
+//                    the chosen logits only.  Mode 1 (scores): s = softmax(z) over all experts, the `top` largest of
+//                    s + correction are chosen, weights = the chosen s over their sum (+ 1e-20)
+//                    Experts from `n_real` on have no matrices (identity experts: their output is their input): their
+//                    slots get no position (slot -> position = -1) and `moe_combine` adds weight * input for them
+//   relu_squared     out = max(x, 0)^2, optionally times sigmoid(one number per row)
 //   moe_sort         the (row, choice) slots grouped by expert, each expert's list padded to whole tiles of 32 (or 128)
 //                    positions; tile -> expert, position -> row, position -> slot (-1: padding) and slot -> position
 //   gather_rows      out[position] = a[row of the position] (zeros at padding): the operand of a product that reads
@@ -23,11 +27,43 @@ namespace {
 
 constexpr int TM = 32, TN = 64, TK = 32;
 
+__device__ __forceinline__ void route_row_scores(const float* __restrict__ z, int n_experts, int top, const float* __restrict__ correction,
+                                                 int* __restrict__ mine, float* __restrict__ wt) {
+  float top_z = -INFINITY, total = 0.f;
+  for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z[e]);
+  for (int e = 0; e < n_experts; ++e) total += expf(z[e] - top_z);
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.f;
+    int at = -1;
+    for (int e = 0; e < n_experts; ++e) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken = taken || mine[j] == e;
+      const float sc = expf(z[e] - top_z) / total;
+      const float v = sc + (correction ? correction[e] : 0.f);
+      if (!taken && (at < 0 || v > best)) {
+        best = v;
+        best_s = sc;
+        at = e;
+      }
+    }
+    mine[k] = at;
+    wt[k] = best_s;
+    sum += best_s;
+  }
+  for (int k = 0; k < top; ++k) wt[k] /= sum + 1e-20f;
+}
+
 __device__ __forceinline__ void route_row(const float* __restrict__ logits, int64_t ld, int r, int n_experts, int top,
-                                          int* __restrict__ chosen, float* __restrict__ weight) {
+                                          int* __restrict__ chosen, float* __restrict__ weight, int mode = 0,
+                                          const float* __restrict__ correction = nullptr) {
   const float* z = logits + (int64_t)r * ld;
   int* mine = chosen + (int64_t)r * top;
   float* wt = weight + (int64_t)r * top;
+  if (mode == 1) {
+    route_row_scores(z, n_experts, top, correction, mine, wt);
+    return;
+  }
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = -1;
@@ -65,7 +101,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows,
                 int* __restrict__ tile_expert, int* __restrict__ pos_row, int* __restrict__ pos_slot, int* __restrict__ slot_pos,
-                const float* __restrict__ logits, int64_t ld_logits, float* __restrict__ weight) {
+                const float* __restrict__ logits, int64_t ld_logits, float* __restrict__ weight, int mode,
+                const float* __restrict__ correction, int n_real) {
   extern __shared__ int sm[];
   int* counts = sm;
   int* offsets = sm + n_experts;
@@ -76,13 +113,14 @@ moe_sort_kernel(int* __restrict__ chosen, int n_slots, int top, int n_experts, i
   for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) pos_row[i] = pos_slot[i] = -1;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
   if (logits != nullptr)                       // the routing itself first, a thread per row: one launch instead of two
-    for (int r = threadIdx.x; r < n_slots / top; r += blockDim.x) route_row(logits, ld_logits, r, n_experts, top, chosen, weight);
+    for (int r = threadIdx.x; r < n_slots / top; r += blockDim.x) route_row(logits, ld_logits, r, n_experts, top, chosen, weight, mode, correction);
   __syncthreads();
-  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) atomicAdd(&counts[chosen[i]], 1);
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x)
+    if (chosen[i] < n_real) atomicAdd(&counts[chosen[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int tile = 0;
-    for (int e = 0; e < n_experts; ++e) {
+    for (int e = 0; e < n_real; ++e) {
       offsets[e] = tile * tile_rows;
       const int n = (counts[e] + tile_rows - 1) / tile_rows;
       for (int t = 0; t < n; ++t) tile_expert[tile + t] = e;
@@ -92,6 +130,10 @@ moe_sort_kernel(int* __restrict__ chosen, int n_slots, int top, int n_experts, i
   __syncthreads();
   for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
     const int e = chosen[i];
+    if (e >= n_real) {                  // an expert without matrices: nothing to multiply
+      slot_pos[i] = -1;
+      continue;
+    }
     const int at = offsets[e] + atomicAdd(&cursor[e], 1);
     pos_row[at] = i / top;
     pos_slot[at] = i;
@@ -335,9 +377,27 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, con
   }
 }
 
+// out = max(x, 0)^2, times sigmoid(row_gate[r * ld_gate]) where a gate is given (one number per row).
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, int64_t ld_x, T* __restrict__ out, int64_t ld_o, const T* __restrict__ row_gate,
+                                    int64_t ld_gate, int n_rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    const float v = fmaxf(to_f32(x[r * ld_x + c]), 0.f);
+    float y = v * v;
+    if (row_gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(row_gate[r * ld_gate])));
+    out[r * ld_o + c] = from_f32<T>(y);
+  }
+}
+
 // Four neighbouring columns a thread (widths and strides in fours, 16-byte aligned bases); the choices in the same order.
+template <typename T>
 __global__ void moe_combine_vec_kernel(float* __restrict__ residual, const float* __restrict__ outs, int64_t ld_outs,
-                                       const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top) {
+                                       const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top,
+                                       const T* __restrict__ input, int64_t ld_in) {
   pdl_launch_dependents();
   pdl_wait();
   const int per_row = width / 4;
@@ -348,7 +408,10 @@ __global__ void moe_combine_vec_kernel(float* __restrict__ residual, const float
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top; ++k) {
       const float wk = weight[r * top + k];
-      const float4 v = *reinterpret_cast<const float4*>(outs + (int64_t)slot_pos[r * top + k] * ld_outs + c);
+      const int at = slot_pos[r * top + k];
+      float4 v;
+      if (at >= 0) v = *reinterpret_cast<const float4*>(outs + (int64_t)at * ld_outs + c);
+      else v = make_float4(to_f32(input[r * ld_in + c]), to_f32(input[r * ld_in + c + 1]), to_f32(input[r * ld_in + c + 2]), to_f32(input[r * ld_in + c + 3]));
       acc.x = fmaf(wk, v.x, acc.x); acc.y = fmaf(wk, v.y, acc.y); acc.z = fmaf(wk, v.z, acc.z); acc.w = fmaf(wk, v.w, acc.w);
     }
     float4* at = reinterpret_cast<float4*>(residual + r * width + c);
@@ -358,15 +421,20 @@ __global__ void moe_combine_vec_kernel(float* __restrict__ residual, const float
   }
 }
 
+template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ outs, int64_t ld_outs,
-                                   const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top) {
+                                   const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top,
+                                   const T* __restrict__ input, int64_t ld_in) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t total = (int64_t)n_rows * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / width, c = i - r * width;
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weight[r * top + k], outs[(int64_t)slot_pos[r * top + k] * ld_outs + c], acc);
+    for (int k = 0; k < top; ++k) {
+      const int at = slot_pos[r * top + k];
+      acc = fmaf(weight[r * top + k], at >= 0 ? outs[(int64_t)at * ld_outs + c] : to_f32(input[r * ld_in + c]), acc);
+    }
     residual[i] += acc;
   }
 }
@@ -392,14 +460,15 @@ KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int 
 // logits given: the rows are routed first (`chosen` and `weight` are written), then grouped.
 KVAD_EXPORT int kvad_moe_sort(int* chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows, int* tile_expert,
                               int* pos_row, int* pos_slot, int* slot_pos, const float* logits, int64_t ld_logits, float* weight,
-                              cudaStream_t stream) {
+                              int mode, const float* correction, int n_real, cudaStream_t stream) {
+  KVAD_REQUIRE((mode == 0 || mode == 1) && n_real >= 0 && n_real <= n_experts, "moe_sort: bad routing mode or expert counts");
   KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096 && tile_rows > 0, "moe_sort: bad sizes");
   KVAD_REQUIRE(logits == nullptr || (weight != nullptr && top <= n_experts && ld_logits >= n_experts), "moe_sort: routing needs weights to write");
-  KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_experts, "moe_sort: %d tiles cannot hold %d slots of %d experts",
+  KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_real, "moe_sort: %d tiles cannot hold %d slots of %d experts",
                max_tiles, n_slots, n_experts);
   if (n_slots == 0) return KVAD_OK;
   kvad_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, chosen, n_slots, top, n_experts, max_tiles,
-              tile_rows, tile_expert, pos_row, pos_slot, slot_pos, logits, ld_logits, weight);
+              tile_rows, tile_expert, pos_row, pos_slot, slot_pos, logits, ld_logits, weight, mode, correction, n_real);
   KVAD_CHECK_LAUNCH("moe_sort");
   return KVAD_OK;
 }
@@ -481,17 +550,41 @@ KVAD_EXPORT int kvad_gather_rows(int dtype, const void* a, int64_t ld_a, const i
   return KVAD_OK;
 }
 
+// input (of `in_dtype`, may be null where every slot has a position): the rows the experts read, for slots without a position.
 KVAD_EXPORT int kvad_moe_combine(float* residual, const float* outs, int64_t ld_outs, const int* slot_pos, const float* weight, int n_rows,
-                                 int width, int top, cudaStream_t stream) {
+                                 int width, int top, int in_dtype, const void* input, int64_t ld_in, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && outs && slot_pos && weight, "moe_combine: bad arguments");
   if (n_rows == 0) return KVAD_OK;
-  if (width % 4 == 0 && ld_outs % 4 == 0 && ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(outs)) & 15) == 0)
-    kvad_launch(moe_combine_vec_kernel, dim3(flat_blocks((int64_t)n_rows * (width / 4), 256)), dim3(256), 0, stream, residual, outs, ld_outs,
-                slot_pos, weight, n_rows, width, top);
-  else
-    kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, outs, ld_outs, slot_pos,
-                weight, n_rows, width, top);
+  const bool vec = width % 4 == 0 && ld_outs % 4 == 0 && ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(outs)) & 15) == 0;
+  dim3 grid(vec ? flat_blocks((int64_t)n_rows * (width / 4), 256) : flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (in_dtype == KVAD_DTYPE_BF16) {
+    if (vec) kvad_launch(moe_combine_vec_kernel<__nv_bfloat16>, grid, block, 0, stream, residual, outs, ld_outs, slot_pos, weight, n_rows, width, top,
+                         (const __nv_bfloat16*)input, ld_in);
+    else kvad_launch(moe_combine_kernel<__nv_bfloat16>, grid, block, 0, stream, residual, outs, ld_outs, slot_pos, weight, n_rows, width, top,
+                     (const __nv_bfloat16*)input, ld_in);
+  } else {
+    if (vec) kvad_launch(moe_combine_vec_kernel<float>, grid, block, 0, stream, residual, outs, ld_outs, slot_pos, weight, n_rows, width, top,
+                         (const float*)input, ld_in);
+    else kvad_launch(moe_combine_kernel<float>, grid, block, 0, stream, residual, outs, ld_outs, slot_pos, weight, n_rows, width, top,
+                     (const float*)input, ld_in);
+  }
   KVAD_CHECK_LAUNCH("moe_combine");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_relu_squared(int dtype, const void* x, int64_t ld_x, void* out, int64_t ld_o, const void* row_gate, int64_t ld_gate,
+                                  int n_rows, int width, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && x && out, "relu_squared: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(relu_squared_kernel<float>, grid, block, 0, stream, (const float*)x, ld_x, (float*)out, ld_o, (const float*)row_gate, ld_gate, n_rows, width);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(relu_squared_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ld_x, (__nv_bfloat16*)out, ld_o,
+                (const __nv_bfloat16*)row_gate, ld_gate, n_rows, width);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "relu_squared: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("relu_squared");
   return KVAD_OK;
 }
 

@@ -7,8 +7,14 @@
 //                     leaves the scaled sum to the next reader of the stream
 //   rotary            pairs of a head's first `dims` entries turned by position * base^(-2i/dims), either
 //                     entry i with i + dims/2 ("half") or 2i with 2i + 1 ("interleaved")
-//   gate_mul          out = act(a) * b,  act = silu or sigmoid
+//                     (`inverse`: by the negative angle; `head_gate`: each head's turned entries times the sigmoid
+//                     of one number per row and head)
+//   gate_mul          out = act(a) * b,  act = silu, sigmoid or relu
 //   scale_add         x += mult * delta; delta = 0
+//   postnorm_rmsnorm  x += g * delta / rms(delta); delta = 0; y = rmsnorm(x)   - a block that norms a sublayer's result
+//                     before it scales it into the stream leaves that to the next reader of the stream (y may be absent)
+//   head_gate         x[r, h, :] *= sigmoid(gate[r, h])
+//   stream_concat     out = [x | x0] in the compute dtype: two 32-bit streams side by side as one product's input
 #include "common.cuh"
 
 using namespace kvad;
@@ -119,7 +125,7 @@ template <typename T>
 __global__ void rotary_kernel(const T* __restrict__ src, int64_t ld_src, int head_stride_src, int off_src,
                               T* __restrict__ dst, int64_t ld_dst, int head_stride_dst, int off_dst,
                               const int* __restrict__ row_pos, const float* __restrict__ inv_freq, int n_rows, int n_heads,
-                              int dims, int interleaved) {
+                              int dims, int interleaved, int inverse, const T* __restrict__ head_gate, int64_t ld_gate) {
   pdl_launch_dependents();
   pdl_wait();
   const int half = dims / 2;
@@ -131,9 +137,12 @@ __global__ void rotary_kernel(const T* __restrict__ src, int64_t ld_src, int hea
     T* d = dst + (int64_t)r * ld_dst + (int64_t)h * head_stride_dst + off_dst;
     float sn, cs;
     sincosf((float)row_pos[r] * inv_freq[p], &sn, &cs);
+    if (inverse) sn = -sn;
+    float g = 1.f;
+    if (head_gate != nullptr) g = sigmoid_f(to_f32(head_gate[(int64_t)r * ld_gate + h]));
     const float u = to_f32(s[a]), v = to_f32(s[b]);
-    d[a] = from_f32<T>(u * cs - v * sn);
-    d[b] = from_f32<T>(v * cs + u * sn);
+    d[a] = from_f32<T>((u * cs - v * sn) * g);
+    d[b] = from_f32<T>((v * cs + u * sn) * g);
   }
 }
 
@@ -147,7 +156,80 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, int64_t ld_a, const T* 
     const int r = (int)(i / width), c = (int)(i % width);
     const float g = to_f32(a[(int64_t)r * ld_a + c]);
     const float v = to_f32(b[(int64_t)r * ld_b + c]);
-    out[(int64_t)r * ld_out + c] = from_f32<T>((act == 0 ? silu_f(g) : sigmoid_f(g)) * v);
+    out[(int64_t)r * ld_out + c] = from_f32<T>((act == 0 ? silu_f(g) : act == 1 ? sigmoid_f(g) : fmaxf(g, 0.f)) * v);
+  }
+}
+
+// x += g * delta / rms(delta) on the 32-bit stream (g: one 32-bit number per column), then y = rmsnorm(x) with `w`
+// (y absent: only the sum).  With `write_back` (all rows are walked) the sum replaces x and delta is cleared; with a
+// row list nothing is written back.  Two sums of squares per row, each in column order through the same tree.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const float* __restrict__ g, float eps_post, int write_back,
+                        const int* __restrict__ row_index, const void* __restrict__ w, int w_f32, int unit_offset,
+                        TO* __restrict__ out, int64_t ld_out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int64_t src = (int64_t)(row_index ? row_index[r] : r) * width;
+  float* xr = x + src;
+  float* dr = delta + src;
+  float sq = 0.f;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    const float v = dr[c];
+    sq = fmaf(v, v, sq);
+  }
+  sq = block_sum(sq, scratch);
+  const float inv_d = 1.0f / sqrtf(sq / (float)width + eps_post);
+  float sq_x = 0.f;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    const float v = fmaf(dr[c] * inv_d, g[c], xr[c]);
+    if (write_back) {
+      xr[c] = v;
+      dr[c] = 0.f;
+    }
+    sq_x = fmaf(v, v, sq_x);
+  }
+  if (out == nullptr) return;
+  sq_x = block_sum(sq_x, scratch);
+  const float inv = 1.0f / sqrtf(sq_x / (float)width + eps);
+  TO* o = out + (int64_t)r * ld_out;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    const float v = write_back ? xr[c] : fmaf(dr[c] * inv_d, g[c], xr[c]);      // (the thread reads what it wrote)
+    float gain = 1.f;
+    if (w != nullptr) gain = load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f);
+    o[c] = from_f32<TO>(v * inv * gain);
+  }
+}
+
+// x[r, h * dv + d] *= sigmoid(gate[r, h]): one number per row and head.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, int64_t ld_x, const T* __restrict__ gate, int64_t ld_gate, int n_rows, int n_heads, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int width = n_heads * dv;
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width;
+    const int c = (int)(i - r * width);
+    T* at = x + r * ld_x + c;
+    *at = from_f32<T>(to_f32(*at) * sigmoid_f(to_f32(gate[r * ld_gate + c / dv])));
+  }
+}
+
+template <typename T>
+__global__ void stream_concat_kernel(const float* __restrict__ x, const float* __restrict__ x0, T* __restrict__ out, int n_rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    out[r * 2 * width + c] = from_f32<T>(x[i]);
+    out[r * 2 * width + width + c] = from_f32<T>(x0[i]);
   }
 }
 
@@ -207,7 +289,8 @@ KVAD_EXPORT int kvad_scale_add(float* x, float* delta, float mult, int64_t total
 
 KVAD_EXPORT int kvad_rotary(int dtype, const void* src, int64_t ld_src, int head_stride_src, int off_src, void* dst,
                             int64_t ld_dst, int head_stride_dst, int off_dst, const int* row_pos, const float* inv_freq,
-                            int n_rows, int n_heads, int dims, int interleaved, cudaStream_t stream) {
+                            int n_rows, int n_heads, int dims, int interleaved, int inverse, const void* head_gate,
+                            int64_t ld_gate, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && dims > 0 && dims % 2 == 0, "rotary: bad sizes rows=%d heads=%d dims=%d", n_rows, n_heads, dims);
   KVAD_REQUIRE(row_pos != nullptr && inv_freq != nullptr, "rotary: needs positions and frequencies");
   if (n_rows == 0) return KVAD_OK;
@@ -215,20 +298,21 @@ KVAD_EXPORT int kvad_rotary(int dtype, const void* src, int64_t ld_src, int head
   dim3 grid(flat_blocks(total, 256)), block(256);
   if (dtype == KVAD_DTYPE_F32)
     kvad_launch(rotary_kernel<float>, grid, block, 0, stream, (const float*)src, ld_src, head_stride_src, off_src, (float*)dst, ld_dst,
-                head_stride_dst, off_dst, row_pos, inv_freq, n_rows, n_heads, dims, interleaved);
+                head_stride_dst, off_dst, row_pos, inv_freq, n_rows, n_heads, dims, interleaved, inverse, (const float*)head_gate, ld_gate);
   else if (dtype == KVAD_DTYPE_BF16)
     kvad_launch(rotary_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)src, ld_src, head_stride_src, off_src,
-                (__nv_bfloat16*)dst, ld_dst, head_stride_dst, off_dst, row_pos, inv_freq, n_rows, n_heads, dims, interleaved);
+                (__nv_bfloat16*)dst, ld_dst, head_stride_dst, off_dst, row_pos, inv_freq, n_rows, n_heads, dims, interleaved, inverse,
+                (const __nv_bfloat16*)head_gate, ld_gate);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "rotary: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("rotary");
   return KVAD_OK;
 }
 
-// act: 0 = silu, 1 = sigmoid.
+// act: 0 = silu, 1 = sigmoid, 2 = relu.
 KVAD_EXPORT int kvad_gate_mul(int dtype, const void* a, int64_t ld_a, const void* b, int64_t ld_b, void* out, int64_t ld_out,
                               int n_rows, int width, int act, cudaStream_t stream) {
-  KVAD_REQUIRE(n_rows >= 0 && width > 0 && (act == 0 || act == 1), "gate_mul: bad arguments rows=%d width=%d act=%d", n_rows, width, act);
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && act >= 0 && act <= 2, "gate_mul: bad arguments rows=%d width=%d act=%d", n_rows, width, act);
   if (n_rows == 0) return KVAD_OK;
   dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
   if (dtype == KVAD_DTYPE_F32)
@@ -239,6 +323,51 @@ KVAD_EXPORT int kvad_gate_mul(int dtype, const void* a, int64_t ld_a, const void
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "gate_mul: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("gate_mul");
+  return KVAD_OK;
+}
+
+// out null: only x += g * delta / rms(delta) (and delta = 0).
+KVAD_EXPORT int kvad_postnorm_rmsnorm(int out_dtype, float* x, float* delta, const float* g, float eps_post, int write_back,
+                                      const int* row_index, const void* w, int w_f32, int unit_offset, void* out, int64_t ld_out,
+                                      int n_rows, int width, float eps, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && x != nullptr && delta != nullptr && g != nullptr, "postnorm_rmsnorm: bad arguments");
+  KVAD_REQUIRE(!(write_back && row_index), "postnorm_rmsnorm: writing back goes with walking all rows");
+  KVAD_REQUIRE(out == nullptr || ld_out >= width, "postnorm_rmsnorm: the output's rows are too short");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(n_rows), block(128);
+  if (out_dtype == KVAD_DTYPE_F32)
+    kvad_launch(postnorm_rmsnorm_kernel<float>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32, unit_offset,
+                (float*)out, ld_out, width, eps);
+  else if (out_dtype == KVAD_DTYPE_BF16)
+    kvad_launch(postnorm_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32,
+                unit_offset, (__nv_bfloat16*)out, ld_out, width, eps);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "postnorm_rmsnorm: unknown dtype %d", out_dtype);
+  KVAD_CHECK_LAUNCH("postnorm_rmsnorm");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_head_gate(int dtype, void* x, int64_t ld_x, const void* gate, int64_t ld_gate, int n_rows, int n_heads, int dv,
+                               cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && dv > 0 && x && gate, "head_gate: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * n_heads * dv, 256)), block(256);
+  if (dtype == KVAD_DTYPE_F32) kvad_launch(head_gate_kernel<float>, grid, block, 0, stream, (float*)x, ld_x, (const float*)gate, ld_gate, n_rows, n_heads, dv);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(head_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)x, ld_x, (const __nv_bfloat16*)gate, ld_gate, n_rows, n_heads, dv);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "head_gate: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("head_gate");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_stream_concat(int dtype, const float* x, const float* x0, void* out, int n_rows, int width, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && x && x0 && out, "stream_concat: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (dtype == KVAD_DTYPE_F32) kvad_launch(stream_concat_kernel<float>, grid, block, 0, stream, x, x0, (float*)out, n_rows, width);
+  else if (dtype == KVAD_DTYPE_BF16) kvad_launch(stream_concat_kernel<__nv_bfloat16>, grid, block, 0, stream, x, x0, (__nv_bfloat16*)out, n_rows, width);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "stream_concat: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("stream_concat");
   return KVAD_OK;
 }
 

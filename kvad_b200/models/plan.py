@@ -5,7 +5,10 @@ embedding, one `PartSpec` per block (so layers may differ in mixer and
 feed-forward), the head, and the ORDER in which blocks run.  The order is a
 list of `LayerCall(layer, cache, writes_cache)`: a block may be named twice
 (its weights run twice, each call with a cache entry of its own), and a call
-may read the cache entry another call writes.  `Model` builds the parts from
+may read the cache entry another call writes.  A block that keeps something
+of its own per sequence besides its mixer's (the inputs of a short
+convolution) gets a second entry, `aux`; `turn` tells a block which pass of a
+repeated range of layers the call belongs to.  `Model` builds the parts from
 the plan through the part registries, collects their tensor requests for the
 audit, loads them, and runs a step.
 """
@@ -26,6 +29,8 @@ class LayerCall:
     layer: int                 # which block's weights
     cache: int                 # which cache entry its mixer uses
     writes_cache: bool = True  # False: reads what another call wrote to that entry
+    aux: Optional[int] = None  # cache entry for what the block itself keeps per sequence (`Block.cache_need`), if anything
+    turn: int = 0              # which pass of a repeated range of layers this call belongs to
 
 
 @dataclass(frozen=True)
@@ -66,11 +71,20 @@ class Model:
 
     # -- cache needs -------------------------------------------------------------
     def _cache_layout(self) -> CacheLayout:
-        n_entries = 1 + max((c.cache for c in self.plan.order), default=-1)
+        n_entries = 1 + max((max(c.cache, -1 if c.aux is None else c.aux) for c in self.plan.order), default=-1)
         needs: list = [None] * n_entries
         written = [False] * n_entries
         for call in self.plan.order:
-            need = self.blocks[call.layer].mixer.cache_need()
+            block = self.blocks[call.layer]
+            own = block.cache_need()
+            if own is not None:
+                if call.aux is None or call.aux == call.cache or needs[call.aux] is not None:
+                    raise ValueError(f"block {call.layer} keeps something of its own: its call needs a cache entry `aux` that no other call uses")
+                needs[call.aux] = own
+                written[call.aux] = True
+            if block.mixer is None:
+                continue
+            need = block.mixer.cache_need()
             if needs[call.cache] is not None and needs[call.cache] != need:
                 raise ValueError(f"cache entry {call.cache} is used by mixers with different needs")
             needs[call.cache] = need

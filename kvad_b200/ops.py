@@ -89,7 +89,11 @@ _SIGNATURES = {
                                   c_int, c_int, c_float, c_void_p],
         "kvad_scale_add": [c_void_p, c_void_p, c_float, c_int64, c_void_p],
         "kvad_rotary": [c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                        c_int, c_int, c_void_p],
+                        c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
+        "kvad_postnorm_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+                                  c_int, c_int, c_float, c_void_p],
+        "kvad_head_gate": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
+        "kvad_stream_concat": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "kvad_gate_mul": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     },
     "attention_scored": {
@@ -123,12 +127,21 @@ _SIGNATURES = {
     "moe": {
         "kvad_moe_tile_rows": [],
         "kvad_moe_route": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                          c_int, c_void_p, c_int, c_void_p],
+        "kvad_relu_squared": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p],
         "kvad_gather_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
         "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_void_p],
         "kvad_clamped_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p],
-        "kvad_moe_combine": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "kvad_moe_combine": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
+    },
+    "channel_recurrence": {
+        "kvad_residual_conv": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_conv_keep": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "kvad_min_gru": [c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_void_p],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -203,6 +216,7 @@ _FAMILY_LIBRARIES = {
     "retention": {"any": ("retention",)},
     "gated_recurrence": {"any": ("gated_recurrence",)},
     "moe": {"any": ("moe",)},
+    "channel_recurrence": {"any": ("channel_recurrence",)},
 }
 
 
@@ -678,11 +692,21 @@ class Ops:
         _check(h.kvad_zero_bytes(_ptr(t), t.numel() * t.element_size(), _stream()), h)
 
     def rotary(self, src, dst, row_pos, inv_freq, n_heads: int, dims: int, *, interleaved: bool, head_stride_src: int,
-               offset_src: int = 0, head_stride_dst: Optional[int] = None, offset_dst: Optional[int] = None) -> None:
+               offset_src: int = 0, head_stride_dst: Optional[int] = None, offset_dst: Optional[int] = None, inverse: bool = False,
+               head_gate=None) -> None:
         """Turns the pairs of `dims` entries of each of `n_heads` heads of every row by the row's position times
         `inv_freq[pair]` (32-bit angles): head h's entries start at column h * head_stride + offset.  `dst` may be
-        `src` (in place) or another buffer (a copy that turns).  `interleaved`: pairs (2i, 2i+1), else (i, i + dims/2)."""
-        _need_cuda(src, dst, row_pos, inv_freq)
+        `src` (in place) or another buffer (a copy that turns).  `interleaved`: pairs (2i, 2i+1), else (i, i + dims/2).
+        `inverse`: by the negative angle.  `head_gate` [rows, heads]: the turned entries of head h are also multiplied by
+        sigmoid(head_gate[r, h])."""
+        _need_cuda(src, dst, row_pos, inv_freq, head_gate)
+        ld_g = 0
+        if head_gate is not None:
+            ld_g = _rows_view(head_gate, "rotary head gate")
+            if head_gate.dtype != self.dtype or head_gate.shape != (src.shape[0], n_heads):
+                raise KernelError("rotary: the head gate must be [rows, heads] of the compute dtype")
+            if dims != (head_stride_src if head_stride_dst is None else head_stride_dst):
+                raise KernelError("rotary: a head gate goes with heads that are turned whole")
         ld_s, ld_d = _rows_view(src, "rotary input"), _rows_view(dst, "rotary output")
         hs_d = head_stride_src if head_stride_dst is None else head_stride_dst
         off_d = offset_src if offset_dst is None else offset_dst
@@ -694,9 +718,58 @@ class Ops:
             raise KernelError("rotary: the heads do not fit the rows")
         h = lib("norm_rotary")
         _check(h.kvad_rotary(self.code, _ptr(src), ld_s, int(head_stride_src), int(offset_src), _ptr(dst), ld_d, int(hs_d), int(off_d),
-                             _ptr(row_pos), _ptr(inv_freq), n, int(n_heads), int(dims), int(bool(interleaved)), _stream()), h)
+                             _ptr(row_pos), _ptr(inv_freq), n, int(n_heads), int(dims), int(bool(interleaved)), int(bool(inverse)),
+                             _ptr(head_gate), ld_g, _stream()), h)
 
-    GATES = {"silu": 0, "sigmoid": 1}
+    def postnorm_rmsnorm(self, x, delta, gain, eps_post: float, out=None, weight=None, eps: float = 0.0, *, unit_offset: bool = False,
+                         rows=None) -> None:
+        """x += gain * delta / sqrt(mean(delta^2) + eps_post) per row of the 32-bit stream (`gain`: float32, one per column),
+        and, where `out` is given, out = rmsnorm(x) with `weight` and `eps`.  With all rows walked (`rows` None) the sum
+        replaces x and delta is cleared; with a row list only `out` is written."""
+        _need_cuda(x, delta, gain, out, weight, rows)
+        width = x.shape[1]
+        if (x.dtype != torch.float32 or delta.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous()
+                or gain.dtype != torch.float32 or gain.numel() != width):
+            raise KernelError("postnorm_rmsnorm: the contiguous float32 stream, a sum of its shape and a float32 gain per column")
+        n, ld_out, w_f32, code = x.shape[0], 0, 0, self.code
+        if out is not None:
+            n, ld_out, code = out.shape[0], _rows_view(out, "postnorm_rmsnorm output"), _code(out.dtype)
+            if out.shape[1] != width:
+                raise KernelError("postnorm_rmsnorm: the output must be as wide as the stream")
+            if weight is not None:
+                if weight.numel() != width or weight.dtype not in (torch.float32, torch.bfloat16):
+                    raise KernelError("postnorm_rmsnorm: the weight must have the row's width, float32 or bfloat16")
+                w_f32 = 1 if weight.dtype == torch.float32 else 0
+        elif rows is not None:
+            raise KernelError("postnorm_rmsnorm: a row list goes with an output")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n):
+            raise KernelError("postnorm_rmsnorm: row list must be int32, one per output row")
+        if rows is None and x.shape[0] < n:
+            raise KernelError("postnorm_rmsnorm: fewer stream rows than output rows")
+        h = lib("norm_rotary")
+        _check(h.kvad_postnorm_rmsnorm(code, _ptr(x), _ptr(delta), _ptr(gain), float(eps_post), 1 if rows is None else 0, _ptr(rows),
+                                       _ptr(weight), w_f32, int(unit_offset), _ptr(out), ld_out, n, width, float(eps), _stream()), h)
+
+    def head_gate(self, x, gate, n_heads: int) -> None:
+        """In place: head h of every row of x times sigmoid(gate[r, h]) (`gate` [rows, heads])."""
+        _need_cuda(x, gate)
+        ld_x, ld_g = _rows_view(x, "head_gate rows"), _rows_view(gate, "head gate")
+        if {x.dtype, gate.dtype} != {self.dtype} or gate.shape != (x.shape[0], n_heads) or x.shape[1] % n_heads:
+            raise KernelError(f"head_gate: rows of whole heads and a gate [rows, heads], both {self.dtype}")
+        h = lib("norm_rotary")
+        _check(h.kvad_head_gate(self.code, _ptr(x), ld_x, _ptr(gate), ld_g, x.shape[0], int(n_heads), x.shape[1] // n_heads, _stream()), h)
+
+    def stream_concat(self, x, x0, out) -> None:
+        """out = [x | x0] in the compute dtype (x, x0: float32 [rows, width], contiguous; out [rows, 2 width], contiguous)."""
+        _need_cuda(x, x0, out)
+        n, width = x.shape
+        if (x.dtype != torch.float32 or x0.dtype != torch.float32 or x0.shape != x.shape or not x.is_contiguous() or not x0.is_contiguous()
+                or out.dtype != self.dtype or out.shape != (n, 2 * width) or not out.is_contiguous()):
+            raise KernelError(f"stream_concat: two contiguous float32 streams of one shape into [rows, 2 width] of {self.dtype}")
+        h = lib("norm_rotary")
+        _check(h.kvad_stream_concat(self.code, _ptr(x), _ptr(x0), _ptr(out), n, width, _stream()), h)
+
+    GATES = {"silu": 0, "sigmoid": 1, "relu": 2}
 
     def gate_mul(self, gate, value, out, act: str = "silu") -> None:
         """out = act(gate) * value, element by element (`gate`, `value`: views of equal shape, 32-bit arithmetic)."""
@@ -993,12 +1066,20 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_moe_route(_ptr(logits), _rows_view(logits, "router logits"), n, E, int(top), _ptr(chosen), _ptr(weight), _stream()), h)
 
-    def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos, *, logits=None, weight=None) -> None:
+    ROUTINGS = {"top_logits": 0, "scores": 1}
+
+    def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos, *, logits=None, weight=None,
+                 routing: str = "top_logits", correction=None, n_real: Optional[int] = None) -> None:
         """Groups the (row, choice) slots of `chosen` [rows, top] by expert, every expert's list padded to whole tiles of
         `tile_rows` positions: `tile_expert` [tiles] (-1: unused), `pos_row` / `pos_slot` [tiles x tile_rows] (-1: padding),
         `slot_pos` [rows x top]: where each slot went.  With `logits` and `weight` the same launch routes the rows first
-        (as `moe_route` does) and writes `chosen` and `weight`."""
-        _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos, logits, weight)
+        (as `moe_route` does) and writes `chosen` and `weight`.  `routing` "scores": the scores are the softmax over all
+        experts, the `top` largest of score + `correction` (float32, one per expert, or None) are chosen and weigh their
+        scores over the chosen scores' sum.  `n_real` < `n_experts`: the experts from `n_real` on have no matrices; their
+        slots get no position (`slot_pos` -1)."""
+        _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos, logits, weight, correction)
+        if correction is not None and (correction.dtype != torch.float32 or correction.numel() != n_experts):
+            raise KernelError("moe_sort: the correction is float32, one per expert")
         ld_z = 0
         if logits is not None:
             ld_z = _rows_view(logits, "router logits")
@@ -1012,7 +1093,8 @@ class Ops:
             raise KernelError("moe_sort: int32 lists, a tile's rows per tile, a place per slot")
         h = lib("moe")
         _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, int(tile_rows), _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot),
-                               _ptr(slot_pos), _ptr(logits), ld_z, _ptr(weight), _stream()), h)
+                               _ptr(slot_pos), _ptr(logits), ld_z, _ptr(weight), self.ROUTINGS[routing], _ptr(correction),
+                               int(n_experts if n_real is None else n_real), _stream()), h)
 
     def gather_rows(self, a, pos_row, out) -> None:
         """out[p] = a[pos_row[p]], zeros where pos_row[p] < 0."""
@@ -1063,9 +1145,15 @@ class Ops:
         _check(h.kvad_clamped_glu(self.code, _ptr(gate), ld_g, _ptr(up), ld_u, _ptr(out), ld_o, gate.shape[0], gate.shape[1], float(limit),
                                   float(alpha), _stream()), h)
 
-    def moe_combine(self, residual, outs, slot_pos, weight) -> None:
-        """residual[r] += sum_k weight[r, k] * outs[slot_pos[r * top + k]], the choices in order (all float32)."""
-        _need_cuda(residual, outs, slot_pos, weight)
+    def moe_combine(self, residual, outs, slot_pos, weight, identity_input=None) -> None:
+        """residual[r] += sum_k weight[r, k] * outs[slot_pos[r * top + k]], the choices in order (all float32); a slot
+        without a position (-1: an expert whose output is its input) adds weight[r, k] * identity_input[r]."""
+        _need_cuda(residual, outs, slot_pos, weight, identity_input)
+        ld_in, in_code = 0, F32
+        if identity_input is not None:
+            ld_in, in_code = _rows_view(identity_input, "the experts' input"), _code(identity_input.dtype)
+            if identity_input.shape != residual.shape:
+                raise KernelError("moe_combine: the experts' input must have the stream's shape")
         n, width = residual.shape
         top = weight.shape[1]
         if (any(t.dtype != torch.float32 for t in (residual, outs, weight)) or not residual.is_contiguous() or not weight.is_contiguous()
@@ -1073,7 +1161,67 @@ class Ops:
             raise KernelError("moe_combine: float32 stream [rows, width], expert outputs [positions, width], weights [rows, top], int32 places")
         h = lib("moe")
         _check(h.kvad_moe_combine(_ptr(residual), _ptr(outs), _rows_view(outs, "expert outputs"), _ptr(slot_pos), _ptr(weight), n, width, top,
-                                  _stream()), h)
+                                  in_code, _ptr(identity_input), ld_in, _stream()), h)
+
+    def relu_squared(self, x, out, row_gate=None) -> None:
+        """out = max(x, 0)^2, times sigmoid(row_gate[r]) where `row_gate` [rows, 1] is given (32-bit arithmetic)."""
+        _need_cuda(x, out, row_gate)
+        ld_x, ld_o, ld_g = _rows_view(x, "relu_squared input"), _rows_view(out, "relu_squared output"), 0
+        if x.shape != out.shape or {x.dtype, out.dtype} != {self.dtype}:
+            raise KernelError(f"relu_squared: needs two {self.dtype} tensors of one shape")
+        if row_gate is not None:
+            if row_gate.dtype != self.dtype or row_gate.dim() != 2 or row_gate.shape != (x.shape[0], 1):
+                raise KernelError("relu_squared: the row gate is [rows, 1] of the compute dtype")
+            ld_g = row_gate.stride(0)
+        h = lib("moe")
+        _check(h.kvad_relu_squared(self.code, _ptr(x), ld_x, _ptr(out), ld_o, _ptr(row_gate), ld_g, x.shape[0], x.shape[1], _stream()), h)
+
+    # -- mixing over time channel by channel ---------------------------------------------------
+    def residual_conv(self, x, taps, out, state, state_off: int, row_seq, row_pos, seq_starts, seq_slots, *, shift: bool = False) -> None:
+        """out = x + (causal convolution over time per channel of x) with `taps` [channels, n]: the last tap meets the row
+        itself, inputs before the step's rows come from the sequence's kept inputs (`state[slot, state_off:]` as
+        [n - 1, channels], 32-bit), zeros before position 0.  `shift`: every sequence brings ONE row and the kept inputs
+        are moved on by it in the same launch (otherwise `conv_keep` does that afterwards)."""
+        _need_cuda(x, taps, out, state, row_seq, row_pos, seq_starts, seq_slots)
+        ld_x, ld_o = _rows_view(x, "residual_conv input"), _rows_view(out, "residual_conv output")
+        C, n_taps = taps.shape
+        if ({x.dtype, taps.dtype, out.dtype} != {self.dtype} or not taps.is_contiguous() or x.shape != out.shape or x.shape[1] != C
+                or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < state_off + (n_taps - 1) * C):
+            raise KernelError(f"residual_conv: needs {self.dtype} rows and taps [channels, n] and a float32 state with room for the kept inputs")
+        h = lib("channel_recurrence")
+        _check(h.kvad_residual_conv(self.code, _ptr(x), ld_x, _ptr(taps), _ptr(out), ld_o, _ptr(state), state.stride(0), int(state_off),
+                                    _ptr(row_seq), _ptr(row_pos), _ptr(seq_starts), _ptr(seq_slots), x.shape[0], C, n_taps, int(bool(shift)),
+                                    _stream()), h)
+
+    def conv_keep(self, x, n_taps: int, state, state_off: int, seq_starts, seq_slots, n_seqs: int) -> None:
+        """Keeps every sequence's last `n_taps` - 1 rows of x (older ones from what was kept) for the next step."""
+        _need_cuda(x, state, seq_starts, seq_slots)
+        ld_x, C = _rows_view(x, "conv_keep input"), x.shape[1]
+        if x.dtype != self.dtype or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < state_off + (n_taps - 1) * C:
+            raise KernelError("conv_keep: rows of the compute dtype and a float32 state with room for the kept inputs")
+        h = lib("channel_recurrence")
+        _check(h.kvad_conv_keep(self.code, _ptr(x), ld_x, _ptr(state), state.stride(0), int(state_off), _ptr(seq_starts), _ptr(seq_slots),
+                                int(n_seqs), C, int(n_taps), _stream()), h)
+
+    @staticmethod
+    def min_gru_chunks(max_new: int) -> int:
+        """Into how many chunks, walked side by side, the minGRU cuts a sequence's rows of a step: by the longest run of
+        new rows only (one row: one chunk; from 16 rows a chunk on, up to 32 chunks)."""
+        return max(1, min(32, max_new // 16))
+
+    def min_gru(self, zug, width: int, out, state, seq_starts, seq_slots, n_seqs: int, max_new: int, *, state_off: int = 0) -> None:
+        """Per sequence and channel over the step's rows in order: S = (1 - z) S + z c with z = sigmoid(a), c = u + 1/2 where
+        u >= 0 and sigmoid(u) where u < 0; out = S * silu(g).  `zug` float32 [rows, 3 width] = a | u | g; `state` float32
+        [slots, >= state_off + width] is carried on."""
+        _need_cuda(zug, out, state, seq_starts, seq_slots)
+        ld, ld_o = _rows_view(zug, "min_gru projections"), _rows_view(out, "min_gru output")
+        if (zug.dtype != torch.float32 or zug.shape[1] < 3 * width or out.dtype != self.dtype or out.shape != (zug.shape[0], width)
+                or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < state_off + width):
+            raise KernelError(f"min_gru: float32 projections [rows, 3 width], {self.dtype} output [rows, width], float32 state")
+        h = lib("channel_recurrence")
+        _check(h.kvad_min_gru(self.code, _ptr(zug), ld, 0, int(width), 2 * int(width), _ptr(out), ld_o, _ptr(state), state.stride(0),
+                              int(state_off), _ptr(seq_starts), _ptr(seq_slots), int(n_seqs), int(width), self.min_gru_chunks(max_new),
+                              _stream()), h)
 
     # -- sampling ------------------------------------------------------------------
     ARGMAX_CHUNK = 2048

@@ -121,17 +121,23 @@ class ShapedScoreAttention(Mixer):
     `value_blend`: "source" - this layer's values are kept for the step (`ctx.shared`) so that later layers can
     blend with them; "blend" - the values stored and attended over are (1 - b) v + b v_source with b this
     layer's scalar `blend_name`; a "source" layer's own scalar is asked for and not used.  `gate`: the heads'
-    outputs are multiplied by sigmoid(W_g h) before the output projection.  The four projections are tensors of
-    their own (`[out, in]`, no biases) and run as one product."""
+    outputs are multiplied by sigmoid(W_g h) before the output projection - entry by entry (True) or, with
+    `gate="head"`, by one number per head.  `position`: a rotary encoding that turns queries and keys before the
+    keys are kept.  `value_position`: a rotary encoding over the whole value - the value of position j is turned
+    by j before it is kept, and each head's weighted sum at position i is turned back by i (before the gate), so
+    that what a query reads of a value depends on their distance.  `bias_suffix`: q, k, v and the output
+    projection have biases (`<name><suffix>`).  The projections are tensors of their own (`[out, in]`) and run as
+    one product."""
     graph_safe = True
-    kernel_families = ("scored_attention",)
+    kernel_families = ("scored_attention", "norm_rotary")
 
     def __init__(self, prefix: str, width: int, n_heads: int, key_dim: int, score_scale: float,
                  n_kv_heads: Optional[int] = None, value_dim: Optional[int] = None, softcap: Optional[float] = None,
                  slope_span: Optional[float] = None, window: Optional[int] = None, keep_first: int = 0,
                  value_blend: Optional[str] = None, gate: bool = False, q_name: str = "q", k_name: str = "k",
                  v_name: str = "v", gate_name: str = "g", out_name: str = "o", blend_name: str = "vmix",
-                 blend_key: str = "first_values"):
+                 blend_key: str = "first_values", position: Optional[PartSpec] = None, value_position: Optional[PartSpec] = None,
+                 bias_suffix: Optional[str] = None):
         super().__init__(prefix)
         self.width, self.n_heads, self.key_dim = int(width), int(n_heads), int(key_dim)
         self.n_kv_heads = int(n_kv_heads) if n_kv_heads else self.n_heads
@@ -146,19 +152,30 @@ class ShapedScoreAttention(Mixer):
         self.window = int(window) if window else None
         self.keep_first = int(keep_first or 0) if self.window else 0
         self.value_blend, self.blend_name, self.blend_key, self.gated = value_blend, blend_name, blend_key, bool(gate)
+        self.head_gate = gate == "head"
         self.q_width, self.k_width = self.n_heads * self.key_dim, self.n_kv_heads * self.key_dim
         self.v_width, self.o_width = self.n_kv_heads * self.value_dim, self.n_heads * self.value_dim
         maps = [(q_name, self.q_width), (k_name, self.k_width), (v_name, self.v_width)]
         if self.gated:
-            maps.append((gate_name, self.o_width))
-        self.proj = FusedLinear(prefix, self.width, maps)
-        self.out = Linear(prefix + out_name, self.o_width, self.width, bias=False, weight_name="")
+            maps.append((gate_name, self.n_heads if self.head_gate else self.o_width, 8))     # (on a 16-byte boundary)
+        self.proj = FusedLinear(prefix, self.width, maps, pad_to=8 if self.head_gate else 1, bias_suffix=bias_suffix,
+                                biased=(q_name, k_name, v_name))
+        self.out = Linear(prefix + out_name, self.o_width, self.width, bias=bias_suffix is not None, weight_name="",
+                          bias_name=bias_suffix or "bias")
+        self.position = build_part("position", position, prefix) if position is not None else None
+        self.value_position = build_part("position", value_position, prefix) if value_position is not None else None
+        if self.position is not None and self.position.dims > self.key_dim:
+            raise ValueError("attention: the rotary encoding turns more entries than a key has")
+        if self.value_position is not None and self.value_position.dims != self.value_dim:
+            raise ValueError("attention: the values' rotary encoding turns the whole value")
+        if self.value_position is not None and self.value_blend:
+            raise ValueError("attention: turned values and blended values do not go together")
         self.blend = None
         group = self.n_heads // self.n_kv_heads
         self.heads_per_block = max(d for d in (1, 2, 4) if group % d == 0)      # prompts; single-token rows take the whole group
 
     def children(self):
-        return [self.proj, self.out]
+        return [self.proj, self.out] + [p for p in (self.position, self.value_position) if p is not None]
 
     def own_requests(self):
         return [TensorRequest(self.prefix + self.blend_name, ())] if self.value_blend else []
@@ -179,6 +196,11 @@ class ShapedScoreAttention(Mixer):
         self.proj.forward(ctx, h, buf)
         q, k, v = (buf[:, self.proj.columns(i)] for i in range(3))
         gate = buf[:, self.proj.columns(3)] if self.gated else None
+        if self.position is not None:      # queries and keys lie side by side, heads of one size: one launch turns both
+            qk = buf[:, :self.q_width + self.k_width]
+            self.position.rotate_heads(ctx, qk, qk, self.n_heads + self.n_kv_heads, self.key_dim)
+        if self.value_position is not None:
+            self.value_position.rotate_heads(ctx, v, v, self.n_kv_heads, self.value_dim)
         view = ctx.kv(call.cache)
         other = None
         if self.value_blend == "source":
@@ -199,8 +221,13 @@ class ShapedScoreAttention(Mixer):
             scratch = ctx.buffer((n * self.n_heads * splits * (self.value_dim + 2),), torch.float32) if splits > 1 else None
         ops.attention_scored(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
                              view.v_pages, self.n_heads, self.score_scale, softcap=self.softcap, slope_span=self.slope_span,
-                             window=self.window or 0, keep_first=self.keep_first, gate=gate,
+                             window=self.window or 0, keep_first=self.keep_first, gate=None if self.head_gate else gate,
                              heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch)
+        if self.value_position is not None:       # the heads' sums are turned back by the rows' own positions, then gated
+            self.value_position.rotate_heads(ctx, mixed, mixed, self.n_heads, self.value_dim, inverse=True,
+                                             head_gate=gate if self.head_gate else None)
+        elif self.head_gate:
+            ctx.ops.head_gate(mixed, gate, self.n_heads)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

@@ -159,7 +159,11 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    mixer: Mixer
+    mixer: Optional[Mixer]          # None: a block that only works on the stream (its calls' `cache` is not used)
+
+    def cache_need(self):
+        """What the block itself keeps per sequence besides its mixer's need (its calls name the entry as `aux`)."""
+        return None
 
     def forward(self, ctx, x: torch.Tensor, call) -> None:
         raise NotImplementedError

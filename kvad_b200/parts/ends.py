@@ -23,8 +23,10 @@ class TokenEmbedding(Part):
     graph_safe = True
 
     def __init__(self, prefix: str, vocab_size: int, width: int, name: str = "wte.weight",
-                 position: Optional[PartSpec] = None, norm: Optional[PartSpec] = None, norm_name: str = "embed.norm"):
+                 position: Optional[PartSpec] = None, norm: Optional[PartSpec] = None, norm_name: str = "embed.norm",
+                 keep_output: bool = False):
         super().__init__(prefix)
+        self.keep_output = bool(keep_output)    # a copy of what the embedding leaves stays in `ctx.shared["embedding_output"]`
         self.vocab_size, self.width, self.name = int(vocab_size), int(width), name
         self.weight: Optional[torch.Tensor] = None
         self.position = build_part("position", position, prefix) if position is not None else None
@@ -52,10 +54,16 @@ class TokenEmbedding(Part):
         table = self.position.table() if self.position is not None else None
         if self.norm is None:
             ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, x)
-            return x
-        looked_up = ctx.buffer((ctx.n_rows, self.width), torch.float32)
-        ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, looked_up)
-        self.norm.forward(ctx, looked_up, n_rows=ctx.n_rows, out=x)       # (the stream stays 32-bit)
+        else:
+            looked_up = ctx.buffer((ctx.n_rows, self.width), torch.float32)
+            ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, looked_up)
+            self.norm.forward(ctx, looked_up, n_rows=ctx.n_rows, out=x)       # (the stream stays 32-bit)
+        if self.keep_output:                    # (the blocks change the stream in place: what they are to see later is a second copy)
+            kept = ctx.shared["embedding_output"] = ctx.buffer((ctx.n_rows, self.width), torch.float32)
+            if self.norm is None:
+                ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, kept)
+            else:
+                self.norm.forward(ctx, looked_up, n_rows=ctx.n_rows, out=kept)
         return x
 
 

@@ -61,12 +61,13 @@ class FusedLinear(Part):
     """Several linear maps of one input, stored as tensors of their own (`[out, in]` each) and held as ONE
     matrix, rows one map after another: one product gives all of them, each a range of columns of the output
     (`columns(i)`).  A map given as (name, size, align) starts at a column that is a multiple of `align` (rows of
-    zeros fill the gap), `pad_to` rounds the whole up the same way; with `bias_suffix` every map has a bias
-    tensor `<name><bias_suffix>`."""
+    zeros fill the gap), `pad_to` rounds the whole up the same way; with `bias_suffix` every map (or, with
+    `biased`, every map named there) has a bias tensor `<name><bias_suffix>`; the others' bias entries are zero."""
     graph_safe = True
 
-    def __init__(self, prefix: str, in_features: int, parts, pad_to: int = 1, bias_suffix: Optional[str] = None):
+    def __init__(self, prefix: str, in_features: int, parts, pad_to: int = 1, bias_suffix: Optional[str] = None, biased=None):
         super().__init__(prefix)
+        self.biased = None if biased is None else {str(n) for n in biased}
         self.in_features = int(in_features)
         self.names = [str(p[0]) for p in parts]
         self.sizes = [int(p[1]) for p in parts]
@@ -85,8 +86,11 @@ class FusedLinear(Part):
     def own_requests(self):
         out = [TensorRequest(self.prefix + n, (o, self.in_features)) for n, o in zip(self.names, self.sizes)]
         if self.bias_suffix is not None:
-            out += [TensorRequest(self.prefix + n + self.bias_suffix, (o,)) for n, o in zip(self.names, self.sizes)]
+            out += [TensorRequest(self.prefix + n + self.bias_suffix, (o,)) for n, o in zip(self.names, self.sizes) if self._has_bias(n)]
         return out
+
+    def _has_bias(self, name: str) -> bool:
+        return self.bias_suffix is not None and (self.biased is None or name in self.biased)
 
     def load_own(self, fetch):
         mats = [fetch(self.prefix + n) for n in self.names]
@@ -97,10 +101,11 @@ class FusedLinear(Part):
             for m, lo in zip(mats, self.offsets):
                 self.weight[lo:lo + m.shape[0]] = m
         if self.bias_suffix is not None:
-            vecs = [fetch(self.prefix + n + self.bias_suffix, keep_f32=True).float() for n in self.names]
-            self.bias = torch.zeros(self.out_features, dtype=torch.float32, device=vecs[0].device)
-            for b, lo in zip(vecs, self.offsets):
-                self.bias[lo:lo + b.numel()] = b
+            self.bias = torch.zeros(self.out_features, dtype=torch.float32, device=self.weight.device)
+            for n, lo in zip(self.names, self.offsets):
+                if self._has_bias(n):
+                    b = fetch(self.prefix + n + self.bias_suffix, keep_f32=True).float()
+                    self.bias[lo:lo + b.numel()] = b
 
     def own_tensors(self):
         return [t for t in (self.weight, self.bias) if t is not None]

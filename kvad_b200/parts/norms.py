@@ -13,6 +13,15 @@ from ..weights.source import TensorRequest
 from .base import Norm, register_part
 
 
+class PostNorm:
+    """How a sublayer's result enters the stream where it is normed first: x += gain * result / rms(result); `gain` is
+    the norm's weight (times a block's gain per channel, if it has one), 32-bit.  Stands in the place of the
+    multiplier in `ctx.shared["deferred_residual"]`."""
+
+    def __init__(self, gain: torch.Tensor, eps: float):
+        self.gain, self.eps = gain, float(eps)
+
+
 class LayerNorm(Norm):
     graph_safe = True
 
@@ -79,8 +88,12 @@ class RMSNorm(Norm):
             deferred = None
         if deferred is not None:
             _, delta, mult = deferred
-            ctx.ops.rmsnorm(x[:ctx.n_rows], self.weight, self.eps, out, unit_offset=self.unit_offset, rows=rows,
-                            deferred=(delta, mult))
+            if isinstance(mult, PostNorm):
+                ctx.ops.postnorm_rmsnorm(x[:ctx.n_rows], delta[:ctx.n_rows], mult.gain, mult.eps, out, self.weight, self.eps,
+                                         unit_offset=self.unit_offset, rows=rows)
+            else:
+                ctx.ops.rmsnorm(x[:ctx.n_rows], self.weight, self.eps, out, unit_offset=self.unit_offset, rows=rows,
+                                deferred=(delta, mult))
             if rows is None:                      # the sum is in the stream now
                 ctx.shared.pop("deferred_residual")
         else:

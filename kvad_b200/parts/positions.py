@@ -65,11 +65,12 @@ class Rotary(PositionEncoding):
         return getattr(fetch, "device", "cuda")
 
     def rotate_heads(self, ctx, src, dst, n_heads: int, head_stride_src: int, offset_src: int = 0,
-                     head_stride_dst=None, offset_dst=None) -> None:
-        """Turns `dims` entries of each head of every row of `src` into `dst` (which may be `src`)."""
+                     head_stride_dst=None, offset_dst=None, inverse: bool = False, head_gate=None) -> None:
+        """Turns `dims` entries of each head of every row of `src` into `dst` (which may be `src`); `inverse`: back, by
+        the negative angle; `head_gate` [rows, heads]: the turned entries also times sigmoid(gate) of their head."""
         ctx.ops.rotary(src, dst, ctx.row_pos, self.inv_freq, n_heads, self.dims, interleaved=self.interleaved,
                        head_stride_src=head_stride_src, offset_src=offset_src, head_stride_dst=head_stride_dst,
-                       offset_dst=offset_dst)
+                       offset_dst=offset_dst, inverse=inverse, head_gate=head_gate)
 
     def rotate(self, ctx, q, k) -> None:
         """In place on queries and keys whose heads are as long as `head_dim` = their width / heads; used by

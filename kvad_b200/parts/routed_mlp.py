@@ -11,6 +11,13 @@ sizes of its own) runs for every row and is added.  The (row, choice) pairs are 
 the experts' two products run as grouped products over those lists (`csrc/moe.cu`); how many tiles a step can need
 follows from its shape alone, so the launches never depend on the routing.  The chosen experts' outputs are summed
 choice by choice in a fixed order.
+
+`score_routed_mlp`: experts of the plain form out = W_down act(W_up h), act = the square of relu, no biases, chosen by
+scores: s = softmax(W_router h) over ALL router outputs (32-bit), the `top` largest of s + `correction` are chosen (the
+correction only steers the choice), and the chosen weigh in with their s over the sum of the chosen s (+ 1e-20).  The
+last `identity` router outputs are experts without matrices whose output is their input.  An optional shared expert of
+the same form runs for every row, times sigmoid(w_sg . h), one number per row.  Same grouping, grouped products and
+ordered sum as `routed_mlp`.
 """
 from __future__ import annotations
 
@@ -112,5 +119,85 @@ class RoutedMLP(FeedForward):
             self.shared.forward(ctx, h, residual)
 
 
+class ScoreRoutedMLP(FeedForward):
+    graph_safe = True
+    kernel_families = ("moe",)
+
+    def __init__(self, prefix: str, width: int, n_experts: int, top: int, hidden: int, identity: int = 0, shared: Optional[dict] = None,
+                 router_name: str = "router", correction_name: Optional[str] = "correction", expert_name: str = "e{}.",
+                 shared_name: str = "shared.", up_name: str = "up", down_name: str = "down", shared_gate_name: str = "sg"):
+        super().__init__(prefix)
+        self.width, self.n_experts, self.identity, self.top, self.hidden = int(width), int(n_experts), int(identity), int(top), int(hidden)
+        self.n_routes = self.n_experts + self.identity
+        if not (1 <= self.top <= self.n_routes) or self.n_experts < 0 or self.identity < 0:
+            raise ValueError(f"score_routed_mlp: every row uses {top} of {self.n_routes} experts")
+        self.router = Linear(prefix + router_name, self.width, self.n_routes, bias=False, weight_name="")
+        self.names = dict(expert=expert_name, up=up_name, down=down_name, correction=correction_name)
+        self.shared_hidden = int(shared["hidden"]) if shared else 0
+        if shared:      # the shared expert's first product also gives its gate: one more row of the same matrix, on a 16-byte boundary
+            self.shared_up = FusedLinear(prefix + shared_name, self.width, [(up_name, self.shared_hidden), (shared_gate_name, 1, 8)], pad_to=8)
+            self.shared_down = Linear(prefix + shared_name + down_name, self.shared_hidden, self.width, bias=False, weight_name="")
+        else:
+            self.shared_up = self.shared_down = None
+        self.w_in = self.w_out = self.correction = None          # [experts, hidden, width], [experts, width, hidden], [routes]
+
+    def children(self):
+        return [self.router] + ([self.shared_up, self.shared_down] if self.shared_up is not None else [])
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(e) + self.names[which]
+
+    def own_requests(self):
+        out = []
+        for e in range(self.n_experts):
+            out += [TensorRequest(self._expert(e, "up"), (self.hidden, self.width)), TensorRequest(self._expert(e, "down"), (self.width, self.hidden))]
+        if self.names["correction"]:
+            out.append(TensorRequest(self.prefix + self.names["correction"], (self.n_routes,)))
+        return out
+
+    def load_own(self, fetch):
+        if self.n_experts:
+            self.w_in = torch.stack([fetch(self._expert(e, "up")) for e in range(self.n_experts)]).contiguous()
+            self.w_out = torch.stack([fetch(self._expert(e, "down")) for e in range(self.n_experts)]).contiguous()
+        if self.names["correction"]:
+            self.correction = fetch(self.prefix + self.names["correction"], keep_f32=True).float().contiguous()
+
+    def own_tensors(self):
+        return [t for t in (self.w_in, self.w_out, self.correction) if t is not None]
+
+    def forward(self, ctx, h, residual):
+        n, ops, E, R, top, ff = h.shape[0], ctx.ops, self.n_experts, self.n_routes, self.top, self.hidden
+        logits = ctx.buffer((n, (R + 3) // 4 * 4), torch.float32)[:, :R]
+        self.router.forward(ctx, h, logits, "store_f32")
+        chosen, weight = ctx.buffer((n, top), torch.int32), ctx.buffer((n, top), torch.float32)
+        tm = ops.moe_tile_rows(n, top, self.width % 8 == 0 and ff % 8 == 0)
+        tiles = max(1, ops.moe_max_tiles(n, top, E, tm))
+        tile_expert, slot_pos = ctx.buffer((tiles,), torch.int32), ctx.buffer((n * top,), torch.int32)
+        pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
+        ops.moe_sort(chosen, R, tm, tile_expert, pos_row, pos_slot, slot_pos, logits=logits, weight=weight, routing="scores",
+                     correction=self.correction, n_real=E)
+        outs = ctx.buffer((tiles * tm, self.width), torch.float32)
+        if E:
+            few = n * top <= ops.MOE_FEW_SLOTS      # (by the step's shape only)
+            hid = ctx.buffer((tiles * tm, ff))
+            if tm == ops.MOE_WIDE_TILE:            # many rows: whole tiles on the tensor cores, from a copy of the rows in position order
+                rows = ctx.buffer((tiles * tm, self.width))
+                ops.gather_rows(h, pos_row, rows)
+                ops.grouped_linear(rows, self.w_in, hid, tile_expert, pos_slot)
+            else:
+                ops.grouped_linear(h, self.w_in, hid, tile_expert, pos_slot, in_rows=pos_row, few_rows=few)
+            ops.relu_squared(hid, hid)
+            ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot, few_rows=few)
+        ops.moe_combine(residual, outs, slot_pos, weight, identity_input=h)
+        if self.shared_up is not None:
+            both = ctx.buffer((n, self.shared_up.out_features))
+            self.shared_up.forward(ctx, h, both)
+            hid = ctx.buffer((n, self.shared_hidden))
+            gate_at = self.shared_up.columns(1).start
+            ops.relu_squared(both[:, :self.shared_hidden], hid, row_gate=both[:, gate_at:gate_at + 1])      # (the gate scales the rows: W (g a) = g W a)
+            self.shared_down.forward(ctx, hid, residual, "residual")
+
+
 register_part("feed_forward", "clamped_glu_mlp", ClampedGluMLP)
+register_part("feed_forward", "score_routed_mlp", ScoreRoutedMLP)
 register_part("feed_forward", "routed_mlp", RoutedMLP)
