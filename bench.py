@@ -271,24 +271,40 @@ def vepinex_config(width, ff, vocab, heads, dim):
             "layers": [dict(l, mlp=mlp) for l in (mem, lat, dlt, mem, lat2, dlt)]}
 
 
+def dopipel_config(width, ff, vocab, heads, dim):
+    """Layers that resemble a real model's: attention with grouped heads and a minGRU, dense and routed feed-forwards in turn (four chosen
+    of eight experts and four identity routes, plus a shared expert; a token's experts together are as wide as the dense `ff`), the
+    first three layers run twice."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                          "rot": {"base": 5e4, "dims": dim}}}
+    gru = {"type": "mingru", "mixer": {"width": width}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 8, "identity": 4, "top": 4}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    layers = [dict(l, mlp=m) for l, m in ((att, dense), (att, moe), (gru, dense), (att, moe), (att, dense), (att, moe))]
+    return {"architecture": "Dopipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 3}, "layers": layers,
+            "loop": {"start": 0, "stop": 3, "times": 2}}
+
+
 def design_points(args, pk, pk_src):
     """`--design nifulix`: prefill and decode throughput of Nifulix at layer sizes that resemble a real model's, beside GPT-2 (the
     closest model this library runs) at the same width, depth, head size and weight count of the feed-forward; and, from
     a kernel-by-kernel pass with CUDA events around every operation, each design's mean time per operation.
-    `--design vepinex`: the same for Vepinex beside Nifulix (recurrent, latent-attention and gated feed-forward layers of its own)."""
+    `--design vepinex`: the same for Vepinex beside Nifulix (recurrent, latent-attention and gated feed-forward layers of its own).
+    `--design dopipel`: the same for Dopipel beside Vepinex (routed feed-forwards, a recurrence and scored attention in both)."""
     import torch
     from kvad_b200 import StepEntry, profile, write_random_model
 
     sizes = {"w1024": dict(width=1024, heads=16, dim=64, ff=2816, inner=4096), "w2048": dict(width=2048, heads=16, dim=128, ff=5632, inner=8192)}
     vocab, ctx, window, plen = 32000, 2048, 512, 512
-    first, second = ("nifulix", "gpt2") if args.design == "nifulix" else ("vepinex", "nifulix")
+    first, second = {"nifulix": ("nifulix", "gpt2"), "vepinex": ("vepinex", "nifulix"), "dopipel": ("dopipel", "vepinex")}[args.design]
     out = {"design": first, "beside": second, "dtype": args.dtype, "data": "synthetic: seeded uniform-random token ids, seeded random weights",
            "prefill": "one step of 2 x 1024 prompt tokens, L2 flushed between iterations", "decode": f"batch {args.batch}, {plen}-token prompts, {min(args.steps, 128)} steps after {max(3, args.warmup)} warm-up steps, tokens fed back on the device",
            "window": window, "sizes": {}}
     for name, z in sizes.items():
         row = {}
         for design in (first, second):
-            cfg = (vepinex_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "vepinex" else
+            cfg = (dopipel_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "dopipel" else
+                   vepinex_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "vepinex" else
                    nifulix_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "nifulix" else
                    dict(model_type="gpt2", n_layer=6, n_embd=z["width"], n_head=z["heads"], n_inner=z["inner"], vocab_size=vocab, n_positions=ctx,
                         layer_norm_epsilon=1e-5, activation_function="gelu_new"))
@@ -396,9 +412,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="the same as --points none")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
                     help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix", "vepinex"],
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix", "vepinex", "dopipel"],
                     help="`nifulix`: instead of the headline, Nifulix beside GPT-2 at equal sizes (prefill, decode, time per operation); "
-                         "`vepinex`: Vepinex beside Nifulix")
+                         "`vepinex`: Vepinex beside Nifulix; `dopipel`: Dopipel beside Vepinex")
     args = ap.parse_args()
     if args.skip_points:
         args.points = "none"
@@ -424,7 +440,7 @@ def main():
     from kvad_b200 import write_random_model
 
     pk, pk_src = peaks()
-    if args.design in ("nifulix", "vepinex"):
+    if args.design in ("nifulix", "vepinex", "dopipel"):
         return design_points(args, pk, pk_src)
     tmp = tempfile.TemporaryDirectory(prefix="kvad_b200-bench-")
     model_dir = tmp.name

@@ -95,7 +95,7 @@ def rotated_value_attention(h, W, p, m):
     """Softmax attention; queries and keys turned on their first rot.dims entries, values turned over all of
     theirs by their own position and the heads' sums turned back by the query's; a sigmoid gate per head."""
     T = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, dk, dv = m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m["vdim"]
     base, rd = m["rot"]["base"], m["rot"]["dims"]
     pos = np.arange(T)
     q = (h @ W[p + "q"].T + W[p + "q.b"]).reshape(T, H, dk)
@@ -148,10 +148,17 @@ def route(h, W, p, top):
     return chosen, w / (w.sum(-1, keepdims=True) + 1e-20), s, pick
 
 
-def mixture(h, W, p, mlp, chosen=None):
-    """`chosen`: take these experts instead of the router's own choice (the weights are still the scores')."""
-    E, n_id, top = mlp["router"]["experts"], mlp["router"].get("identity", 0), mlp["router"]["top"]
-    own, w, s, _ = route(h, W, p, top)
+def mixture(h, W, p, mlp, chosen=None, margins=None, own_out=None):
+    """`chosen`: take these experts instead of the router's own choice (the weights are still the scores').  `margins`
+    receives, row by row, how far the last chosen choice score is above the first one left out; `own_out` the router's
+    own choice."""
+    E, top = mlp["router"]["experts"], mlp["router"]["top"]
+    own, w, s, pick = route(h, W, p, top)
+    if margins is not None:
+        ranked = -np.sort(-pick, axis=-1)
+        margins.append(ranked[:, top - 1] - ranked[:, top] if pick.shape[1] > top else np.full(h.shape[0], np.inf))
+    if own_out is not None:
+        own_out.append(own)
     if chosen is not None:
         w = np.take_along_axis(s, chosen, -1)
         w = w / (w.sum(-1, keepdims=True) + 1e-20)
@@ -183,10 +190,12 @@ def run_order(cfg):
     return out
 
 
-def layer(x, W, cfg, i, routed=None, run=0):
+def layer(x, W, cfg, i, forced=None, margins=None, own=None):
+    """`forced`: an iterator over the experts to take, one array [T, top] per routed feed-forward in run order."""
     L, p, eps = cfg["layers"][i], f"l{i}.", cfg["norm"]["eps"]
     h = rms_norm(x, W[p + "norm1"], eps)
-    h = input_convolution(h, W[p + "canon1"])
+    if cfg.get("canon"):
+        h = input_convolution(h, W[p + "canon1"])
     if L["type"] == "attention":
         y = rotated_value_attention(h, W, p + "mix.", L["mixer"])
     else:
@@ -199,22 +208,32 @@ def layer(x, W, cfg, i, routed=None, run=0):
     if mlp["kind"] == "dense":
         y = relu_glu(h, W, p + "mlp.")
     else:
-        y = mixture(h, W, p + "mlp.", mlp, None if routed is None else routed.get(run))
+        y = mixture(h, W, p + "mlp.", mlp, None if forced is None else next(forced), margins, own)
     return x + rms_norm(y, W[p + "norm2b"], eps) * W[p + "ls2"]
 
 
-def forward(cfg, W, tokens, routed=None, streams=None):
-    """Logits [tokens, vocab] of one whole sequence.  `routed`: {layer run: chosen experts [T, top]} to take
-    instead of the routers' own choices; `streams`: a list that receives the stream after every layer run."""
+def forward(cfg, W, tokens, forced=None, streams=None, margins=None, own=None):
+    """Logits [tokens, vocab] of one whole sequence.  `forced`: the experts to take instead of the routers' own
+    choices, one array [T, top] per routed feed-forward in the order they run; `streams`: a list that receives the
+    stream after every layer run; `margins`, `own`: see `mixture`."""
     x = W["embed"][np.asarray(tokens)]
     x0 = x.copy()
-    for run, (i, t, first) in enumerate(run_order(cfg)):
+    forced = iter(forced) if forced is not None else None
+    for i, t, first in run_order(cfg):
         if first:
             x = np.concatenate([x, x0], axis=-1) @ W["loop.in"].T + W["loop.step"][t]
-        x = layer(x, W, cfg, i, routed, run)
+        x = layer(x, W, cfg, i, forced, margins, own)
         if streams is not None:
             streams.append(x.copy())
     return rms_norm(x, W["final.norm"], cfg["norm"]["eps"]) @ W["head"].T
+
+
+def greedy(cfg, W, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(forward(cfg, W, toks)[-1].argmax()))
+        toks.append(out[-1])
+    return out
 
 
 def load(model_dir):
