@@ -272,17 +272,17 @@ def vepinex_config(width, ff, vocab, heads, dim):
 
 
 def dopipel_config(width, ff, vocab, heads, dim):
-    """Layers that resemble a real model's: attention with grouped heads and a minGRU, dense and routed feed-forwards in turn (four chosen
-    of eight experts and four identity routes, plus a shared expert; a token's experts together are as wide as the dense `ff`), the
-    first three layers run twice."""
+    """Layers that resemble a real model's: attention with grouped heads and minGRUs, routed and dense feed-forwards in turn (two chosen
+    of eight experts and two identity routes, plus a shared expert: a token's experts together are as wide as the dense `ff`, as in
+    `vepinex_config`), layers 1 and 2 run twice."""
     att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                                          "rot": {"base": 5e4, "dims": dim}}}
+                                          "rot": {"base": 1e4, "dims": dim}}}
     gru = {"type": "mingru", "mixer": {"width": width}}
     dense = {"kind": "dense", "ff": ff}
-    moe = {"kind": "moe", "router": {"experts": 8, "identity": 4, "top": 4}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
-    layers = [dict(l, mlp=m) for l, m in ((att, dense), (att, moe), (gru, dense), (att, moe), (att, dense), (att, moe))]
-    return {"architecture": "Dopipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 3}, "layers": layers,
-            "loop": {"start": 0, "stop": 3, "times": 2}}
+    moe = {"kind": "moe", "router": {"experts": 8, "identity": 2, "top": 2}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    layers = [dict(l, mlp=m) for l, m in ((att, moe), (gru, dense), (att, moe), (att, dense), (gru, moe), (att, dense))]
+    return {"architecture": "Dopipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers,
+            "loop": {"start": 1, "stop": 3, "times": 2}}
 
 
 def design_points(args, pk, pk_src):

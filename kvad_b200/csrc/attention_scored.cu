@@ -20,7 +20,8 @@
 // the cache has dropped are never touched.
 //
 // Also here: the cache writes that go with it - keys and values of different sizes with the values blended
-// with another layer's (`kv_store_blend`), and a latent row normalised, its rotary part turned, and stored
+// with another layer's (`kv_store_blend`), queries, keys and values turned by their positions and the keys and values
+// stored in the same pass (`turn_store`), and a latent row normalised, its rotary part turned, and stored
 // (`latent_store`).
 #include "common.cuh"
 
@@ -380,6 +381,72 @@ __global__ void kv_store_blend_kernel(const T* __restrict__ k_src, int64_t ld_k,
   }
 }
 
+// Queries, keys and values of a step's rows, turned by the rows' positions where the layer asks for it, and the keys
+// and values stored: the first `rot_k` entries of every query head are turned in place; every key head likewise on
+// its way to its page; every value head over all its entries (`freq_v` given) or not at all.  A thread owns one unit
+// of a row: a pair that turns, or one entry that passes.  Angles are position x frequency in 32-bit.
+template <typename T>
+__global__ void turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src,
+                                  int64_t ld_v, const float* __restrict__ freq_k, int rot_k, int inter_k,
+                                  const float* __restrict__ freq_v, int inter_v, const int* __restrict__ row_seq,
+                                  const int* __restrict__ row_pos, const int* __restrict__ page_table, int table_width,
+                                  T* __restrict__ k_pages, T* __restrict__ v_pages, int n_rows, int n_heads, int n_kv, int dk, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half_k = rot_k / 2, half_v = dv / 2;
+  const int uq = n_heads * half_k;                         // queries: only the pairs that turn (the rest stay where they are)
+  const int per_k = half_k + (dk - rot_k), uk = n_kv * per_k;
+  const int per_v = freq_v != nullptr ? half_v : dv, uv = n_kv * per_v;
+  const int per_row = uq + uk + uv;
+  const int64_t total = (int64_t)n_rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / per_row), c = (int)(i % per_row);
+    const int pos = row_pos[r];
+    if (c < uq) {
+      const int h = c / half_k, p = c % half_k;
+      const int a = inter_k ? 2 * p : p, b = inter_k ? 2 * p + 1 : p + half_k;
+      T* x = q + (int64_t)r * ld_q + (int64_t)h * dk;
+      float sn, cs;
+      sincosf((float)pos * freq_k[p], &sn, &cs);
+      const float u = to_f32(x[a]), v = to_f32(x[b]);
+      x[a] = from_f32<T>(turn_first(u, v, cs, sn));
+      x[b] = from_f32<T>(turn_second(u, v, cs, sn));
+      continue;
+    }
+    const int64_t page = page_table[(int64_t)row_seq[r] * table_width + pos / PAGE];
+    if (c < uq + uk) {
+      const int ck = c - uq, h = ck / per_k, p = ck % per_k;
+      const T* x = k_src + (int64_t)r * ld_k + (int64_t)h * dk;
+      T* d = k_pages + ((page * n_kv + h) * PAGE + pos % PAGE) * dk;
+      if (p < half_k) {
+        const int a = inter_k ? 2 * p : p, b = inter_k ? 2 * p + 1 : p + half_k;
+        float sn, cs;
+        sincosf((float)pos * freq_k[p], &sn, &cs);
+        const float u = to_f32(x[a]), v = to_f32(x[b]);
+        d[a] = from_f32<T>(turn_first(u, v, cs, sn));
+        d[b] = from_f32<T>(turn_second(u, v, cs, sn));
+      } else {
+        const int e = rot_k + (p - half_k);
+        d[e] = x[e];
+      }
+    } else {
+      const int cv = c - uq - uk, h = cv / per_v, p = cv % per_v;
+      const T* x = v_src + (int64_t)r * ld_v + (int64_t)h * dv;
+      T* d = v_pages + ((page * n_kv + h) * PAGE + pos % PAGE) * dv;
+      if (freq_v != nullptr) {
+        const int a = inter_v ? 2 * p : p, b = inter_v ? 2 * p + 1 : p + half_v;
+        float sn, cs;
+        sincosf((float)pos * freq_v[p], &sn, &cs);
+        const float u = to_f32(x[a]), v = to_f32(x[b]);
+        d[a] = from_f32<T>(turn_first(u, v, cs, sn));
+        d[b] = from_f32<T>(turn_second(u, v, cs, sn));
+      } else {
+        d[p] = x[p];
+      }
+    }
+  }
+}
+
 // A warp per row: the first `rank` entries are RMS-normalised with a weight, the last `rot` entries turned by
 // the row's position (pairs interleaved or half apart), and the row goes to its place in pages of one head of
 // rank + rot entries.
@@ -411,8 +478,8 @@ latent_store_kernel(const T* __restrict__ src, int64_t ld, const void* __restric
     float sn, cs;
     sincosf((float)pos * inv_freq[p], &sn, &cs);
     const float u = to_f32(x[rank + ia]), v = to_f32(x[rank + ib]);
-    dst[rank + ia] = from_f32<T>(u * cs - v * sn);
-    dst[rank + ib] = from_f32<T>(v * cs + u * sn);
+    dst[rank + ia] = from_f32<T>(turn_first(u, v, cs, sn));
+    dst[rank + ib] = from_f32<T>(turn_second(u, v, cs, sn));
   }
 }
 
@@ -528,6 +595,35 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   if (dtype == KVAD_DTYPE_F32) return dispatch_scored<float>(a, n_seqs, max_new, stream);
   if (dtype == KVAD_DTYPE_BF16) return dispatch_scored<__nv_bfloat16>(a, n_seqs, max_new, stream);
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): unknown dtype %d", dtype);
+}
+
+// rot_k: how many entries of a query/key head turn (0: none; even, at most dk); freq_v null: the values are stored as they are,
+// else they turn over all dv entries (dv even).
+KVAD_EXPORT int kvad_turn_store(int dtype, void* q, int64_t ld_q, const void* k_src, int64_t ld_k, const void* v_src, int64_t ld_v,
+                                const float* freq_k, int rot_k, int inter_k, const float* freq_v, int inter_v, const int* row_seq,
+                                const int* row_pos, const int* page_table, int table_width, void* k_pages, void* v_pages, int n_rows,
+                                int n_heads, int n_kv, int dk, int dv, int page_size, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_kv > 0 && dk > 0 && dv > 0 && table_width > 0, "turn_store: bad sizes rows=%d heads=%d kv_heads=%d dk=%d dv=%d",
+               n_rows, n_heads, n_kv, dk, dv);
+  KVAD_REQUIRE(page_size == PAGE, "turn_store: pages of %d positions, not %d", PAGE, page_size);
+  KVAD_REQUIRE(rot_k >= 0 && rot_k % 2 == 0 && rot_k <= dk && (rot_k == 0 || freq_k != nullptr), "turn_store: %d of %d key entries cannot turn in pairs", rot_k, dk);
+  KVAD_REQUIRE(freq_v == nullptr || dv % 2 == 0, "turn_store: values of %d entries cannot turn in pairs", dv);
+  KVAD_REQUIRE(q && k_src && v_src && k_pages && v_pages, "turn_store: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t per_row = (int64_t)n_heads * (rot_k / 2) + (int64_t)n_kv * (rot_k / 2 + dk - rot_k) + (int64_t)n_kv * (freq_v ? dv / 2 : dv);
+  const int64_t total = (int64_t)n_rows * per_row;
+  const int threads = 256;
+  const int64_t want = (total + threads - 1) / threads;
+  dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16)), block(threads);
+#define KVAD_TS(T)                                                                                                                     \
+  kvad_launch(turn_store_kernel<T>, grid, block, 0, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, freq_k, rot_k, inter_k, \
+              freq_v, inter_v, row_seq, row_pos, page_table, table_width, (T*)k_pages, (T*)v_pages, n_rows, n_heads, n_kv, dk, dv)
+  if (dtype == KVAD_DTYPE_F32) KVAD_TS(float);
+  else if (dtype == KVAD_DTYPE_BF16) KVAD_TS(__nv_bfloat16);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "turn_store: unknown dtype %d", dtype);
+#undef KVAD_TS
+  KVAD_CHECK_LAUNCH("turn_store");
+  return KVAD_OK;
 }
 
 KVAD_EXPORT int kvad_kv_store_blend(int dtype, const void* k_src, int64_t ld_k, const void* v_src, int64_t ld_v, const void* v_other,

@@ -141,6 +141,11 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned ran
   return v;
 }
 
+// A pair (u, v) turned by an angle whose cosine and sine are given: one product rounded, then one fused step, spelled
+// out so that every kernel that turns pairs rounds alike.
+__device__ __forceinline__ float turn_first(float u, float v, float cs, float sn) { return __fmaf_rn(u, cs, -__fmul_rn(v, sn)); }
+__device__ __forceinline__ float turn_second(float u, float v, float cs, float sn) { return __fmaf_rn(v, cs, __fmul_rn(u, sn)); }
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -26,6 +26,7 @@ using namespace kvad;
 namespace {
 
 constexpr int TM = 32, TN = 64, TK = 32;
+constexpr int ROUTE_APART_ROWS = 256;      // from this many rows a step on, the routing is a launch of its own over many blocks
 
 __device__ __forceinline__ void route_row_scores(const float* __restrict__ z, int n_experts, int top, const float* __restrict__ correction,
                                                  int* __restrict__ mine, float* __restrict__ wt) {
@@ -89,11 +90,11 @@ __device__ __forceinline__ void route_row(const float* __restrict__ logits, int6
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n_rows, int n_experts, int top,
-                                 int* __restrict__ chosen, float* __restrict__ weight) {
+                                 int* __restrict__ chosen, float* __restrict__ weight, int mode, const float* __restrict__ correction) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r < n_rows) route_row(logits, ld, r, n_experts, top, chosen, weight);
+  if (r < n_rows) route_row(logits, ld, r, n_experts, top, chosen, weight, mode, correction);
 }
 
 // One block.  counts -> padded offsets -> places.  Which place a slot gets inside its expert's list is not fixed
@@ -447,12 +448,14 @@ inline int flat_blocks(int64_t total, int threads) {
 }  // namespace
 
 KVAD_EXPORT int kvad_moe_tile_rows() { return TM; }
+KVAD_EXPORT int kvad_moe_route_apart_rows() { return ROUTE_APART_ROWS; }
 
 KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int n_experts, int top, int* chosen, float* weight,
                                cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && n_experts > 0 && top > 0 && top <= n_experts && ld >= n_experts, "moe_route: bad sizes experts=%d top=%d", n_experts, top);
   if (n_rows == 0) return KVAD_OK;
-  kvad_launch(moe_route_kernel, dim3((n_rows + 63) / 64), dim3(64), 0, stream, logits, ld, n_rows, n_experts, top, chosen, weight);
+  kvad_launch(moe_route_kernel, dim3((n_rows + 63) / 64), dim3(64), 0, stream, logits, ld, n_rows, n_experts, top, chosen, weight, 0,
+              (const float*)nullptr);
   KVAD_CHECK_LAUNCH("moe_route");
   return KVAD_OK;
 }
@@ -467,6 +470,13 @@ KVAD_EXPORT int kvad_moe_sort(int* chosen, int n_slots, int top, int n_experts, 
   KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_real, "moe_sort: %d tiles cannot hold %d slots of %d experts",
                max_tiles, n_slots, n_experts);
   if (n_slots == 0) return KVAD_OK;
+  if (logits != nullptr && n_slots / top >= ROUTE_APART_ROWS) {      // many rows: routed by many blocks first (by the step's shape only)
+    const int n_rows = n_slots / top;
+    kvad_launch(moe_route_kernel, dim3((n_rows + 63) / 64), dim3(64), 0, stream, logits, ld_logits, n_rows, n_experts, top, chosen, weight, mode,
+                correction);
+    KVAD_CHECK_LAUNCH("moe_route");
+    logits = nullptr;
+  }
   kvad_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, chosen, n_slots, top, n_experts, max_tiles,
               tile_rows, tile_expert, pos_row, pos_slot, slot_pos, logits, ld_logits, weight, mode, correction, n_real);
   KVAD_CHECK_LAUNCH("moe_sort");

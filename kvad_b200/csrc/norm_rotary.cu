@@ -141,8 +141,8 @@ __global__ void rotary_kernel(const T* __restrict__ src, int64_t ld_src, int hea
     float g = 1.f;
     if (head_gate != nullptr) g = sigmoid_f(to_f32(head_gate[(int64_t)r * ld_gate + h]));
     const float u = to_f32(s[a]), v = to_f32(s[b]);
-    d[a] = from_f32<T>((u * cs - v * sn) * g);
-    d[b] = from_f32<T>((v * cs + u * sn) * g);
+    d[a] = from_f32<T>(turn_first(u, v, cs, sn) * g);
+    d[b] = from_f32<T>(turn_second(u, v, cs, sn) * g);
   }
 }
 

@@ -102,6 +102,8 @@ _SIGNATURES = {
                                   c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
         "kvad_kv_store_blend": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                            c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_linear_heads": [c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_latent_store": [c_int, c_void_p, c_int64, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                               c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -126,6 +128,7 @@ _SIGNATURES = {
     },
     "moe": {
         "kvad_moe_tile_rows": [],
+        "kvad_moe_route_apart_rows": [],
         "kvad_moe_route": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                           c_int, c_void_p, c_int, c_void_p],
@@ -805,6 +808,32 @@ class Ops:
                                      lam_f32, _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
                                      n, n_kv, dk, dv, page, _stream()), h)
 
+    def turn_store(self, q, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, *, inv_freq=None, dims: int = 0,
+                   interleaved: bool = False, value_inv_freq=None, value_interleaved: bool = False) -> None:
+        """One pass over a step's rows: the first `dims` entries of every query head turned in place by the row's position
+        (pairs (2i, 2i+1) if `interleaved`, else (i, i + dims/2); `inv_freq` one frequency per pair, 32-bit angles), the keys
+        turned likewise on their way into the pages, the values turned over ALL their entries (`value_inv_freq` given) or
+        stored as they are.  What `rotary` on queries and keys, `rotary` on values and `kv_store_blend` do in three."""
+        _need_cuda(q, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, inv_freq, value_inv_freq)
+        ld_q, ld_k, ld_v = _rows_view(q, "queries"), _rows_view(k_src, "keys"), _rows_view(v_src, "values")
+        _, n_kv, page, dk = k_pages.shape
+        dv, n = v_pages.shape[3], q.shape[0]
+        if (q.shape[1] != n_heads * dk or k_src.shape != (n, n_kv * dk) or v_src.shape != (n, n_kv * dv) or v_pages.shape[:3] != k_pages.shape[:3]
+                or {q.dtype, k_src.dtype, v_src.dtype, k_pages.dtype, v_pages.dtype} != {self.dtype} or not k_pages.is_contiguous()
+                or not v_pages.is_contiguous()):
+            raise KernelError(f"turn_store: rows must match the cache's heads and be {self.dtype}")
+        if dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < dims // 2 or dims % 2 or dims > dk):
+            raise KernelError("turn_store: an even number of a key's entries turns, with a float32 frequency per pair")
+        if value_inv_freq is not None and (value_inv_freq.dtype != torch.float32 or dv % 2 or value_inv_freq.numel() < dv // 2):
+            raise KernelError("turn_store: values turn whole: an even size and a float32 frequency per pair")
+        if row_pos.dtype != torch.int32 or row_seq.dtype != torch.int32 or row_pos.numel() < n or row_seq.numel() < n:
+            raise KernelError("turn_store: int32 sequences and positions, one per row")
+        h = lib("attention_scored")
+        _check(h.kvad_turn_store(self.code, _ptr(q), ld_q, _ptr(k_src), ld_k, _ptr(v_src), ld_v, _ptr(inv_freq if dims else None), int(dims),
+                                 int(bool(interleaved)), _ptr(value_inv_freq), int(bool(value_interleaved)), _ptr(row_seq), _ptr(row_pos),
+                                 _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), n, int(n_heads), n_kv, dk, dv, page,
+                                 _stream()), h)
+
     def latent_store(self, src, weight, eps: float, inv_freq, row_seq, row_pos, page_table, pages, rank: int, rot: int, *,
                      interleaved: bool) -> None:
         """Rows `[rows, rank + rot]`: the first `rank` entries RMS-normalised with `weight`, the last `rot` turned by the
@@ -1095,6 +1124,9 @@ class Ops:
         _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, int(tile_rows), _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot),
                                _ptr(slot_pos), _ptr(logits), ld_z, _ptr(weight), self.ROUTINGS[routing], _ptr(correction),
                                int(n_experts if n_real is None else n_real), _stream()), h)
+        if logits is not None and n >= h.kvad_moe_route_apart_rows():
+            global _launches
+            _launches += 1          # many rows: the routing is a launch of its own
 
     def gather_rows(self, a, pos_row, out) -> None:
         """out[p] = a[pos_row[p]], zeros where pos_row[p] < 0."""

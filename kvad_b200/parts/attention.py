@@ -196,20 +196,30 @@ class ShapedScoreAttention(Mixer):
         self.proj.forward(ctx, h, buf)
         q, k, v = (buf[:, self.proj.columns(i)] for i in range(3))
         gate = buf[:, self.proj.columns(3)] if self.gated else None
-        if self.position is not None:      # queries and keys lie side by side, heads of one size: one launch turns both
-            qk = buf[:, :self.q_width + self.k_width]
-            self.position.rotate_heads(ctx, qk, qk, self.n_heads + self.n_kv_heads, self.key_dim)
-        if self.value_position is not None:
-            self.value_position.rotate_heads(ctx, v, v, self.n_kv_heads, self.value_dim)
         view = ctx.kv(call.cache)
         other = None
+        turns = self.position is not None or self.value_position is not None
+        if turns and call.writes_cache and not self.value_blend:      # one launch turns queries, keys and values and stores the latter two
+            pos, vpos = self.position, self.value_position
+            ops.turn_store(q, k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages, self.n_heads,
+                           inv_freq=pos.inv_freq if pos is not None else None, dims=pos.dims if pos is not None else 0,
+                           interleaved=pos is not None and pos.interleaved, value_inv_freq=vpos.inv_freq if vpos is not None else None,
+                           value_interleaved=vpos is not None and vpos.interleaved)
+            stored = True
+        else:
+            if self.position is not None:      # queries and keys lie side by side, heads of one size: one launch turns both
+                qk = buf[:, :self.q_width + self.k_width]
+                self.position.rotate_heads(ctx, qk, qk, self.n_heads + self.n_kv_heads, self.key_dim)
+            if self.value_position is not None:
+                self.value_position.rotate_heads(ctx, v, v, self.n_kv_heads, self.value_dim)
+            stored = False
         if self.value_blend == "source":
             ctx.shared[self.blend_key] = v
         elif self.value_blend == "blend":
             other = ctx.shared.get(self.blend_key)
             if other is None or other.shape != v.shape:
                 raise ValueError("value blending: no layer before this one has left values of this shape")
-        if call.writes_cache:
+        if call.writes_cache and not stored:
             ops.kv_store_blend(k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages,
                                v_other=other, blend=self.blend if other is not None else None)
         mixed = ctx.buffer((n, self.o_width))

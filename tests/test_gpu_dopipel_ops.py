@@ -110,9 +110,9 @@ class Paged:
         self.v_pages = torch.full((n_pages, G, PAGE, dv), float("nan"), device="cuda", dtype=DT[dtype])
 
 
-def attend(ops, dtype, cache, data, spans, m, hp):
-    """Rows [a, a + r) of every sequence as one step, the way the mixer strings the launches: turn queries and keys, turn
-    the values, store, attend, turn the heads' sums back and gate them."""
+def attend(ops, dtype, cache, data, spans, m, hp, fused=True):
+    """Rows [a, a + r) of every sequence as one step, the way the mixer strings the launches: turn queries, keys and
+    values and store the latter two (`fused`: in one launch; else in three), attend, turn the heads' sums back and gate them."""
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     live = [s for s, (_, r) in enumerate(spans) if r]
     cat = dev(np.concatenate([data[s][a:a + r] for s, (a, r) in enumerate(spans) if r]), DT[dtype])
@@ -120,11 +120,15 @@ def attend(ops, dtype, cache, data, spans, m, hp):
     pos = i32(np.concatenate([np.arange(spans[s][0], sum(spans[s])) for s in live]))
     nq, nk, nv = H * dk, G * dk, G * dv
     qk, v, gate = cat[:, :nq + nk], cat[:, nq + nk:nq + nk + nv], cat[:, nq + nk + nv:]
-    ops.rotary(qk, qk, pos, inv_freq(m["rot"]["base"], m["rot"]["dims"]), H + G, m["rot"]["dims"], interleaved=True, head_stride_src=dk)
-    fv = inv_freq(m["rot"]["base"], dv)
-    ops.rotary(v, v, pos, fv, G, dv, interleaved=True, head_stride_src=dv)
+    fk, fv = inv_freq(m["rot"]["base"], m["rot"]["dims"]), inv_freq(m["rot"]["base"], dv)
     table = dev(cache.table[live])
-    ops.kv_store_blend(qk[:, nq:], v, seq, pos, table, cache.k_pages, cache.v_pages)
+    if fused:
+        ops.turn_store(qk[:, :nq], qk[:, nq:], v, seq, pos, table, cache.k_pages, cache.v_pages, H, inv_freq=fk, dims=m["rot"]["dims"],
+                       interleaved=True, value_inv_freq=fv, value_interleaved=True)
+    else:
+        ops.rotary(qk, qk, pos, fk, H + G, m["rot"]["dims"], interleaved=True, head_stride_src=dk)
+        ops.rotary(v, v, pos, fv, G, dv, interleaved=True, head_stride_src=dv)
+        ops.kv_store_blend(qk[:, nq:], v, seq, pos, table, cache.k_pages, cache.v_pages)
     out = torch.full((cat.shape[0], H * dv), float("nan"), device="cuda", dtype=DT[dtype])
     starts = i32(np.concatenate([[0], np.cumsum([spans[s][1] for s in live])]))
     ops.attention_scored(qk[:, :nq], out, starts, i32([sum(spans[s]) for s in live]), len(live), max(r for _, r in spans), table,
@@ -155,13 +159,43 @@ def test_attention_with_turned_values_prompts_portions_and_single_rows(dtype, H,
     cache.k_pages.fill_(float("nan")), cache.v_pages.fill_(float("nan"))
     cuts = [[(0, 2), (2, 61), (63, 2), (65, 60)], [(0, 3), (3, 2), (5, 2), (7, 1)], [(0, 64), (64, 1), (65, 2), (67, 2)]]
     for j in range(4):
-        got = attend(ops, dtype, cache, data, [c[j] for c in cuts], m, hp=1 if j % 2 else max(d for d in (1, 2, 4) if group % d == 0))
+        got = attend(ops, dtype, cache, data, [c[j] for c in cuts], m, hp=1 if j % 2 else max(d for d in (1, 2, 4) if group % d == 0), fused=j < 2)
         for s in range(3):
             a, r = cuts[s][j]
             assert rel(torch.as_tensor(got[s]), want[s][a:a + r]) < tol * max(1.0, np.abs(want[s]).max() / np.abs(want[s][a:a + r]).max()), ("portion", j, s)
     for p in range(125, 150):
-        got = attend(ops, dtype, cache, data, [(p, 1), (0, 0), (0, 0)], m, hp=min(group, 32))
+        got = attend(ops, dtype, cache, data, [(p, 1), (0, 0), (0, 0)], m, hp=min(group, 32), fused=p % 2 == 0)
         assert rel(torch.as_tensor(got[0]), want[0][p:p + 1]) < tol * max(1.0, np.abs(want[0]).max() / np.abs(want[0][p]).max()), ("single", p)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dk,dv,rd,layout,turn_v", [(4, 2, 16, 24, 8, "interleaved", True), (3, 1, 7, 10, 4, "half", True), (2, 2, 12, 5, 12, "half", False),
+                                                        (5, 5, 6, 8, 0, "interleaved", True), (8, 2, 128, 64, 64, "interleaved", False)])
+def test_one_launch_turns_and_stores_what_three_do(dtype, H, G, dk, dv, rd, layout, turn_v):
+    """The fused launch against the single ones, bit for bit: queries in place, keys and values in their pages; a part of a
+    key that does not turn, keys of odd size, values that turn or not, both layouts of pairs."""
+    rng, ops, lens, inter = np.random.default_rng(dk + dv), Ops(DT[dtype]), [130, 5], layout == "interleaved"
+    n = sum(lens)
+    rows = dev(rng.standard_normal((n, H * dk + G * dk + G * dv + 3)), DT[dtype])
+    seq, pos = i32(np.concatenate([[0] * lens[0], [1] * lens[1]])), i32(np.concatenate([np.arange(lens[0]), 700 + np.arange(lens[1])]))
+    fk, fv = (inv_freq(300.0, rd) if rd else None), inv_freq(300.0, dv if dv % 2 == 0 else dv + 1)
+    if dv % 2:
+        turn_v = False
+    caches = [Paged([lens[0], 700 + lens[1]], G, dk, dv, dtype, seed=3) for _ in range(2)]
+    nq, nk = H * dk, G * dk
+    a, b = rows.clone(), rows.clone()
+    ops.turn_store(a[:, :nq], a[:, nq:nq + nk], a[:, nq + nk:nq + nk + G * dv], seq, pos, dev(caches[0].table), caches[0].k_pages, caches[0].v_pages, H,
+                   inv_freq=fk, dims=rd, interleaved=inter, value_inv_freq=fv if turn_v else None, value_interleaved=inter)
+    if rd:
+        ops.rotary(b, b, pos, fk, H + G, rd, interleaved=inter, head_stride_src=dk)
+    vb = b[:, nq + nk:nq + nk + G * dv]
+    if turn_v:
+        ops.rotary(vb, vb, pos, fv, G, dv, interleaved=inter, head_stride_src=dv)
+    ops.kv_store_blend(b[:, nq:nq + nk], vb, seq, pos, dev(caches[1].table), caches[1].k_pages, caches[1].v_pages)
+    assert torch.equal(a[:, :nq], b[:, :nq]) and torch.equal(a[:, nq:], rows[:, nq:])          # (the fused launch leaves keys and values as they came)
+    for x, y in ((caches[0].k_pages, caches[1].k_pages), (caches[0].v_pages, caches[1].v_pages)):
+        assert torch.equal(torch.isnan(x), torch.isnan(y)) and torch.equal(torch.nan_to_num(x), torch.nan_to_num(y))
+    assert int((~torch.isnan(caches[0].k_pages)).sum()) == n * G * dk
 
 
 @pytest.mark.parametrize("mode", ["prompt", "single"])
