@@ -216,6 +216,7 @@ _FAMILY_LIBRARIES = {
     "causal_attention": {"any": ("attention_simt", "attention_decode"), torch.bfloat16: ("attention_prefill",), torch.float32: ()},
     "norm_rotary": {"any": ("norm_rotary",)},
     "scored_attention": {"any": ("attention_scored",)},
+    "prompt_attention": {torch.bfloat16: ("attention_prefill",)},
     "retention": {"any": ("retention",)},
     "gated_recurrence": {"any": ("gated_recurrence",)},
     "moe": {"any": ("moe",)},
@@ -571,6 +572,13 @@ class Ops:
 
     def prefill_takes(self, head_dim: int) -> bool:
         return head_dim in self.PREFILL_HEAD_SIZES
+
+    def prompt_attention_takes(self, q, head_dim: int, page_size: int) -> bool:
+        """Whether prompt rows of a mixer other than the plain causal attention (grouped heads, a scale of its own, but
+        nothing else on the scores, keys as long as values) go to `attention_prefill`: bfloat16, a head size it has,
+        its page size, a positive scale is the caller's; queries on a 16-byte boundary with such a row stride."""
+        return (self.tensor_core_prefill and self.prefill_takes(head_dim) and page_size == 64 and q.dtype == torch.bfloat16
+                and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
 
     def attention_prefill(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages,
                           n_heads: int, scale: float, window: int = 0) -> None:

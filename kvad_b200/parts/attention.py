@@ -173,6 +173,12 @@ class ShapedScoreAttention(Mixer):
         self.blend = None
         group = self.n_heads // self.n_kv_heads
         self.heads_per_block = max(d for d in (1, 2, 4) if group % d == 0)      # prompts; single-token rows take the whole group
+        # scores that nothing shapes, keys as long as values, no gate inside the heads' sums: prompt rows can take the
+        # tensor-core kernel of the plain causal attention (bfloat16; it reads the same pages)
+        self.plain_scores = (not self.softcap and not self.slope_span and self.window is None
+                             and (self.head_gate or not self.gated) and self.key_dim == self.value_dim)
+        if self.plain_scores:
+            self.kernel_families = (*type(self).kernel_families, "prompt_attention")
 
     def children(self):
         return [self.proj, self.out] + [p for p in (self.position, self.value_position) if p is not None]
@@ -229,10 +235,14 @@ class ShapedScoreAttention(Mixer):
             reach = (self.window + self.keep_first) if self.window else view.page_table.shape[1] * view.page_size
             splits = ops.scored_splits(n, self.n_kv_heads, group, reach)
             scratch = ctx.buffer((n * self.n_heads * splits * (self.value_dim + 2),), torch.float32) if splits > 1 else None
-        ops.attention_scored(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
-                             view.v_pages, self.n_heads, self.score_scale, softcap=self.softcap, slope_span=self.slope_span,
-                             window=self.window or 0, keep_first=self.keep_first, gate=None if self.head_gate else gate,
-                             heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch)
+        if (not b.is_decode) and self.plain_scores and ops.prompt_attention_takes(q, self.key_dim, view.page_size):
+            ops.attention_prefill(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
+                                  view.v_pages, self.n_heads, self.score_scale, 0)
+        else:
+            ops.attention_scored(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
+                                 view.v_pages, self.n_heads, self.score_scale, softcap=self.softcap, slope_span=self.slope_span,
+                                 window=self.window or 0, keep_first=self.keep_first, gate=None if self.head_gate else gate,
+                                 heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch)
         if self.value_position is not None:       # the heads' sums are turned back by the rows' own positions, then gated
             self.value_position.rotate_heads(ctx, mixed, mixed, self.n_heads, self.value_dim, inverse=True,
                                              head_gate=gate if self.head_gate else None)

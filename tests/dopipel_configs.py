@@ -64,7 +64,12 @@ CONFIGS = {
                [attention(4, 4, 48, 40, 16, base=1e5), mingru(320), attention(5, 1, 64, 128, 64, base=3e4), mingru(512), attention(8, 2, 32, 32, 8, base=1e5)],
                [moe(32, 2, 4, 64, shared=192), dense(512), moe(12, 4, 3, 96), dense(384), moe(32, 0, 4, 64, shared=64)],
                taps=5, loop=(3, 5, 2)),
+    # keys as long as values, 64 and 128 of them: in bfloat16 prompt rows attend on the tensor cores, single rows do not
+    "F": model(192, 777,
+               [attention(6, 3, 64, 64, 32, base=2e4, scale=0.11), mingru(128), attention(4, 1, 128, 128, 128, base=700.0, scale=0.07)],
+               [dense(256), moe(4, 1, 2, 64, shared=32), None],
+               taps=3, loop=(1, 3, 2)),
 }
-SEEDS = {"A": 111, "B": 212, "C": 313, "D": 414, "E": 515}
-#: the configurations every test of the engine runs on; "E" has tests of its own
+SEEDS = {"A": 111, "B": 212, "C": 313, "D": 414, "E": 515, "F": 616}
+#: the configurations every test of the engine runs on; "E" and "F" have tests of their own
 SMALL = ("A", "B", "C", "D")

@@ -78,6 +78,10 @@ def test_libraries_are_those_of_the_models_parts():
     libs = libraries_for(torch.bfloat16, fams)
     assert {"norm_rotary", "attention_scored", "channel_recurrence", "moe", "linear_tcgen05"} <= set(libs)
     assert not {"attention_prefill", "attention_decode", "attention_simt", "retention", "gated_recurrence"} & set(libs)
+    # keys as long as values: bfloat16 prompts take the prompt kernel of the plain causal attention, 32-bit ones do not
+    fams = Model(arch.plan(arch.read_config(JsonView(CONFIGS["F"])))).kernel_families()
+    assert "attention_prefill" in libraries_for(torch.bfloat16, fams) and "attention_prefill" not in libraries_for(torch.float32, fams)
+    assert not {"attention_decode", "attention_simt"} & set(libraries_for(torch.bfloat16, fams))
 
 
 @pytest.mark.parametrize("change,what", [

@@ -206,6 +206,29 @@ def test_a_long_prompt_in_two_portions_then_a_batch_decoded_over_many_pages(engi
     e.cache.book.check_all_free()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_on_the_tensor_cores_single_rows_beside_them(engine, loaded, dtype):
+    """Heads of 64 and 128 with keys as long as values: in bfloat16 a prompt's rows attend through the tensor-core kernel
+    (two prompts side by side, then portions that begin and end inside a page), single rows through the other kernel,
+    over the same pages; in 32-bit both take one path."""
+    from kvad_b200.ops import libraries_for, prefill_wait_timeouts
+    e = engine("F", dtype)
+    assert ("attention_prefill" in libraries_for(e.dtype, e.model.kernel_families())) == (dtype == "bfloat16")
+    vocab = CONFIGS["F"]["vocab"]
+    a, b = Seq(e, random_tokens(61, 331, vocab)), Seq(e, random_tokens(62, 131, vocab))
+    step(e, [(a, 200, range(200)), (b, 70, range(70))])
+    step(e, [(a, 101, range(101)), (b, 59, range(59))])
+    step(e, [(a, 1, [0]), (b, 1, [0])])
+    step(e, [(a, 1, [0]), (b, 1, [0])])
+    for _ in range(28):
+        step(e, [(a, 1, [0])])
+    a.close(), b.close()
+    verify("F", dtype, loaded, a, b)
+    e.cache.book.check_all_free()
+    if dtype == "bfloat16":
+        assert prefill_wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("name", SMALL)
 def test_the_routers_choices_are_the_oracles_where_its_margin_is_clear(engine, loaded, name):
     """bfloat16: with the engine's choices before it, the oracle chooses the same experts wherever the last chosen

@@ -110,9 +110,10 @@ class Paged:
         self.v_pages = torch.full((n_pages, G, PAGE, dv), float("nan"), device="cuda", dtype=DT[dtype])
 
 
-def attend(ops, dtype, cache, data, spans, m, hp, fused=True):
+def attend(ops, dtype, cache, data, spans, m, hp, fused=True, tensor_cores=False):
     """Rows [a, a + r) of every sequence as one step, the way the mixer strings the launches: turn queries, keys and
-    values and store the latter two (`fused`: in one launch; else in three), attend, turn the heads' sums back and gate them."""
+    values and store the latter two (`fused`: in one launch; else in three), attend (`tensor_cores`: through the prompt
+    kernel of the plain causal attention), turn the heads' sums back and gate them."""
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     live = [s for s, (_, r) in enumerate(spans) if r]
     cat = dev(np.concatenate([data[s][a:a + r] for s, (a, r) in enumerate(spans) if r]), DT[dtype])
@@ -131,8 +132,14 @@ def attend(ops, dtype, cache, data, spans, m, hp, fused=True):
         ops.kv_store_blend(qk[:, nq:], v, seq, pos, table, cache.k_pages, cache.v_pages)
     out = torch.full((cat.shape[0], H * dv), float("nan"), device="cuda", dtype=DT[dtype])
     starts = i32(np.concatenate([[0], np.cumsum([spans[s][1] for s in live])]))
-    ops.attention_scored(qk[:, :nq], out, starts, i32([sum(spans[s]) for s in live]), len(live), max(r for _, r in spans), table,
-                         cache.k_pages, cache.v_pages, H, m["scale"], heads_per_block=hp)
+    if tensor_cores:
+        qq = qk[:, :nq].contiguous()              # (the mixer's rows are padded to 16 bytes; these are not)
+        assert ops.prompt_attention_takes(qq, dk, PAGE)
+        ops.attention_prefill(qq, out, starts, i32([sum(spans[s]) for s in live]), len(live), max(r for _, r in spans), table,
+                              cache.k_pages, cache.v_pages, H, m["scale"], 0)
+    else:
+        ops.attention_scored(qk[:, :nq], out, starts, i32([sum(spans[s]) for s in live]), len(live), max(r for _, r in spans), table,
+                             cache.k_pages, cache.v_pages, H, m["scale"], heads_per_block=hp)
     ops.rotary(out, out, pos, fv, H, dv, interleaved=True, head_stride_src=dv, inverse=True, head_gate=gate)
     o, at, res = out.double().cpu().numpy(), 0, {}
     for s in live:
@@ -196,6 +203,56 @@ def test_one_launch_turns_and_stores_what_three_do(dtype, H, G, dk, dv, rd, layo
     for x, y in ((caches[0].k_pages, caches[1].k_pages), (caches[0].v_pages, caches[1].v_pages)):
         assert torch.equal(torch.isnan(x), torch.isnan(y)) and torch.equal(torch.nan_to_num(x), torch.nan_to_num(y))
     assert int((~torch.isnan(caches[0].k_pages)).sum()) == n * G * dk
+
+
+@pytest.mark.parametrize("H,G,d,rd", [(6, 3, 64, 32), (4, 1, 128, 128), (8, 4, 32, 8), (2, 2, 48, 48)])
+def test_prompt_rows_on_the_tensor_cores_with_turned_values(H, G, d, rd):
+    """Keys as long as values, bfloat16: prompt rows go through the kernel of the plain causal attention (tcgen05 for
+    heads of 64 and 128, mma.sync for the others) between the same turns; whole prompts, then portions over the pages
+    the portions before them wrote."""
+    from kvad_b200.ops import prefill_wait_timeouts
+    rng, ops = np.random.default_rng(H * d), Ops(torch.bfloat16)
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 0.2, "rot": {"base": 300.0, "dims": rd}}
+    lens, W = [150, 9, 70], selection_weights(H, G, d, d)
+    cache = Paged(lens, G, d, d, "bfloat16", seed=d)
+    data = [stored(rng.standard_normal((n, H * d + 2 * G * d + H)), "bfloat16") for n in lens]
+    want = [pl.rotated_value_attention(x, W, "", m) for x in data]
+    tol = angle_tol("bfloat16", 150) * 3
+    got = attend(ops, "bfloat16", cache, data, [(0, n) for n in lens], m, hp=1, tensor_cores=True)
+    for s in range(3):
+        assert rel(torch.as_tensor(got[s]), want[s]) < tol, ("whole", s)
+    cache.k_pages.fill_(float("nan")), cache.v_pages.fill_(float("nan"))
+    cuts = [[(0, 2), (2, 61), (63, 2), (65, 85)], [(0, 3), (3, 2), (5, 2), (7, 2)], [(0, 64), (64, 1), (65, 2), (67, 3)]]
+    for j in range(4):
+        got = attend(ops, "bfloat16", cache, data, [c[j] for c in cuts], m, hp=1, fused=j < 2, tensor_cores=True)
+        for s in range(3):
+            a, r = cuts[s][j]
+            assert rel(torch.as_tensor(got[s]), want[s][a:a + r]) < tol * max(1.0, np.abs(want[s]).max() / np.abs(want[s][a:a + r]).max()), ("portion", j, s)
+    assert prefill_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("marked", [0, 63, 64, 333, 398, 399])
+def test_a_far_value_comes_back_turned_on_the_tensor_cores(marked):
+    """One key's score stands far above the rest; the last query of a prompt must read that key's value turned by the
+    distance between them, through the tensor-core kernel (bfloat16, heads of 64)."""
+    ops, n, d = Ops(torch.bfloat16), 400, 64
+    m = {"heads": 2, "kv_heads": 1, "dim": d, "vdim": d, "scale": 1.0, "rot": {"base": 30.0, "dims": 2}}
+    W = selection_weights(2, 1, d, d)
+    x = np.zeros((n, 2 * d + d + d + 2))
+    x[:, 2], x[:, d + 2] = 32.0, 32.0            # both heads ask along entry 2 (which no turn touches)
+    x[:, 2 * d + 3] = 0.125
+    x[marked, 2 * d + 2] = 1.0
+    x[:, 3 * d:4 * d] = stored(np.random.default_rng(marked).standard_normal((n, d)) * 0.01, "bfloat16")
+    x[marked, 3 * d:3 * d + 6] = [1.0, 0.0, 0.5, -0.5, 0.0, 2.0]
+    x[:, 4 * d:] = 20.0                           # gates open
+    want = pl.rotated_value_attention(x, W, "", m)[-1]
+    turned = pl.turn_pairs(x[marked, 3 * d:4 * d].reshape(1, 1, d), [marked - (n - 1)], 30.0, d)[0, 0]
+    assert np.allclose(want[:d], turned, atol=2e-3)
+    if marked < n - 1:
+        assert np.abs(turned - x[marked, 3 * d:4 * d]).max() > 0.3
+    cache = Paged([n], 1, d, d, "bfloat16", seed=marked)
+    got = attend(ops, "bfloat16", cache, [x], [(0, n)], m, hp=2, tensor_cores=True)[0][-1]
+    assert np.abs(got - want).max() < 0.03
 
 
 @pytest.mark.parametrize("mode", ["prompt", "single"])
