@@ -54,6 +54,78 @@ residual_conv_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict_
   }
 }
 
+// Prompt rows in bfloat16 with up to four taps, channels in 16-byte pieces: a thread owns 8 channels of `rows_each`
+// consecutive rows of the step.  The taps' weights and the window of the last taps - 1 inputs stay in registers; the
+// window is read anew where a row opens another sequence (or the thread's run), so a row costs one 16-byte load and
+// one store.  The sums run in the order of `residual_conv_kernel`: the same bits.
+template <int NT>
+__global__ void __launch_bounds__(64)
+residual_conv_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ taps,
+                          __nv_bfloat16* __restrict__ out, int64_t ld_out, const float* __restrict__ state, int64_t state_stride,
+                          int64_t state_off, const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                          const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, int n_rows, int channels, int rows_each) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int KEEP = NT - 1;
+  const int c = (blockIdx.y * 64 + threadIdx.x) * 8;
+  if (c >= channels) return;
+  float w[NT][8];
+  {
+    __nv_bfloat16 flat[8 * NT];                        // taps[c .. c + 8][0 .. NT): 16 NT bytes on a 16-byte boundary
+#pragma unroll
+    for (int v = 0; v < NT; ++v) *reinterpret_cast<uint4*>(flat + 8 * v) = *reinterpret_cast<const uint4*>(taps + (int64_t)c * NT + 8 * v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < NT; ++j) w[j][i] = __bfloat162float(flat[i * NT + j]);
+  }
+  float win[KEEP > 0 ? KEEP : 1][8];
+  const int r0 = blockIdx.x * rows_each, r1 = min(r0 + rows_each, n_rows);
+  int s_before = -1;
+  for (int r = r0; r < r1; ++r) {
+    const int s = row_seq[r];
+    __nv_bfloat16 in[8];
+    *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(x + (int64_t)r * ld_x + c);
+    if (KEEP > 0 && s != s_before) {
+      const int pos = row_pos[r], first = seq_starts[s], p0 = pos - (r - first);
+      const float* kept = state + (int64_t)seq_slots[s] * state_stride + state_off;
+#pragma unroll
+      for (int j = 0; j < KEEP; ++j) {
+        const int pp = pos - KEEP + j;
+        if (pp >= p0) {
+          __nv_bfloat16 b[8];
+          *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(x + (int64_t)(first + pp - p0) * ld_x + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) win[j][i] = __bfloat162float(b[i]);
+        } else if (pp >= 0) {
+          const float4* k4 = reinterpret_cast<const float4*>(kept + (int64_t)(pp - p0 + KEEP) * channels + c);
+          const float4 a = k4[0], b = k4[1];
+          win[j][0] = a.x, win[j][1] = a.y, win[j][2] = a.z, win[j][3] = a.w;
+          win[j][4] = b.x, win[j][5] = b.y, win[j][6] = b.z, win[j][7] = b.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) win[j][i] = 0.f;
+        }
+      }
+      s_before = s;
+    }
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float own = __bfloat162float(in[i]);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < KEEP; ++j) acc = fmaf(w[j][i], win[j][i], acc);
+      acc = fmaf(w[KEEP][i], own, acc);
+      o[i] = from_f32<__nv_bfloat16>(own + acc);
+#pragma unroll
+      for (int j = 0; j + 1 < KEEP; ++j) win[j][i] = win[j + 1][i];
+      if (KEEP > 0) win[KEEP - 1][i] = own;
+    }
+    *reinterpret_cast<uint4*>(out + (int64_t)r * ld_out + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // A thread per (sequence, channel): the inputs at the sequence's last taps - 1 positions, from this step's rows or,
 // where the step brought fewer, from what was kept before.
 template <typename T>
@@ -136,6 +208,23 @@ KVAD_EXPORT int kvad_residual_conv(int dtype, const void* x, int64_t ld_x, const
   KVAD_REQUIRE(n_rows >= 0 && channels > 0 && n_taps >= 1 && n_taps <= 16, "residual_conv: 1 to 16 taps, got %d", n_taps);
   KVAD_REQUIRE(x && taps && out && state && ld_x >= channels && ld_out >= channels, "residual_conv: bad arguments");
   if (n_rows == 0) return KVAD_OK;
+  const auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (dtype == KVAD_DTYPE_BF16 && !shift && n_taps <= 4 && n_rows >= 64 && channels % 8 == 0 && ld_x % 8 == 0 && ld_out % 8 == 0 &&
+      state_stride % 4 == 0 && state_off % 4 == 0 && !misaligned(x) && !misaligned(out) && !misaligned(taps) && !misaligned(state)) {
+    const int rows_each = 4;
+    dim3 vgrid((n_rows + rows_each - 1) / rows_each, (channels + 511) / 512), vblock(64);
+#define KVAD_CONV_ROWS(NT)                                                                                                          \
+  kvad_launch(residual_conv_rows_kernel<NT>, vgrid, vblock, 0, stream, (const __nv_bfloat16*)x, ld_x, (const __nv_bfloat16*)taps,    \
+              (__nv_bfloat16*)out, ld_out, (const float*)state, state_stride, state_off, row_seq, row_pos, seq_starts, seq_slots,    \
+              n_rows, channels, rows_each)
+    if (n_taps == 1) KVAD_CONV_ROWS(1);
+    else if (n_taps == 2) KVAD_CONV_ROWS(2);
+    else if (n_taps == 3) KVAD_CONV_ROWS(3);
+    else KVAD_CONV_ROWS(4);
+#undef KVAD_CONV_ROWS
+    KVAD_CHECK_LAUNCH("residual_conv");
+    return KVAD_OK;
+  }
   dim3 grid(n_rows, (channels + 511) / 512), block(128);
   if (dtype == KVAD_DTYPE_F32)
     kvad_launch(residual_conv_kernel<float>, grid, block, 0, stream, (const float*)x, ld_x, (const float*)taps, (float*)out, ld_out, state,

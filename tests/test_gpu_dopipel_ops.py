@@ -317,6 +317,36 @@ def test_input_convolution_in_portions_shorter_than_its_taps(dtype, C, taps):
     assert float((state[[1, 3, 5]] - 7.0).abs().max()) == 0.0 and float(state[:, :5].abs().max()) in (0.0, 7.0)      # slots of no sequence, and what lies before the offset
 
 
+@pytest.mark.parametrize("C,taps", [(24, 3), (1000, 4), (64, 2), (520, 1), (512, 4)])
+def test_input_convolution_of_prompt_rows_in_16_byte_pieces(C, taps):
+    """Steps of 64 rows and more in bfloat16 with up to four taps: a thread walks four consecutive rows of 8 channels with
+    the window in registers.  Sequences begin and end inside such a run, portions begin inside a sequence with fewer rows
+    behind them than taps; the result has the bits of the row-by-row kernel (which a state offset of 5 numbers selects)."""
+    rng, ops = np.random.default_rng(C + taps), Ops(torch.bfloat16)
+    lens, slots = [150, 9, 70], [4, 0, 2]
+    w = stored(rng.standard_normal((C, taps)) * 0.5, "bfloat16")
+    x = [stored(rng.standard_normal((n, C)), "bfloat16") for n in lens]
+    want = [pl.input_convolution(a, w) for a in x]
+    states = {off: torch.zeros((6, off + max(1, (taps - 1) * C)), device="cuda") for off in (8, 5)}
+    done = [0, 0, 0]
+    for portion in ([61, 2, 30], [63, 5, 3], [26, 2, 37]):
+        rows = np.concatenate([x[s][done[s]:done[s] + portion[s]] for s in range(3)])
+        starts = np.concatenate([[0], np.cumsum(portion)])
+        seq = np.concatenate([[s] * portion[s] for s in range(3)])
+        pos = np.concatenate([np.arange(done[s], done[s] + portion[s]) for s in range(3)])
+        xin, outs = dev(rows, torch.bfloat16), {}
+        for off, state in states.items():
+            outs[off] = torch.full(rows.shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+            ops.residual_conv(xin, dev(w, torch.bfloat16), outs[off], state, off, i32(seq), i32(pos), i32(starts), i32(slots), shift=False)
+            ops.conv_keep(xin, taps, state, off, i32(starts), i32(slots), 3)
+        ref = np.concatenate([want[s][done[s]:done[s] + portion[s]] for s in range(3)])
+        assert rel(outs[8], ref) < KTOL["bfloat16"], portion
+        assert torch.equal(outs[8], outs[5]), portion
+        for s in range(3):
+            done[s] += portion[s]
+    assert done == lens
+
+
 # ----------------------------------------------------------------------------- minGRU
 def gru_weights(n):
     eye = np.eye(n)
