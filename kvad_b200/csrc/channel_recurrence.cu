@@ -147,57 +147,84 @@ __global__ void conv_keep_kernel(const T* __restrict__ x, int64_t ld_x, float* _
   }
 }
 
+constexpr int GRU_AHEAD = 8;            // rows whose sums a thread fetches before it walks them
+
 __device__ __forceinline__ void gru_terms(float a, float u, float& z, float& cand) {
   z = sigmoid_f(a);
   cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
 }
 
-// Block (32 channels, n_chunks chunks) per (32 channels, sequence).  zug: [rows, ld] with the three projections at
+// Block (W channels, n_chunks chunks) per (W channels, sequence), W = blockDim.x: 32, or 16 where that leaves too few blocks.  zug: [rows, ld] with the three projections at
 // columns off_z, off_u, off_g.
 template <typename T>
 __global__ void __launch_bounds__(1024)
 min_gru_kernel(const float* __restrict__ zug, int64_t ld, int off_z, int off_u, int off_g, T* __restrict__ out, int64_t ld_out,
                float* __restrict__ state, int64_t state_stride, int64_t state_off, const int* __restrict__ seq_starts,
                const int* __restrict__ seq_slots, int width) {
-  extern __shared__ float sm[];            // A [chunks][32], B [chunks][32]
+  extern __shared__ float sm[];            // A [chunks][W], B [chunks][W]
   pdl_launch_dependents();
   pdl_wait();
-  const int s = blockIdx.y, c = blockIdx.x * 32 + threadIdx.x, j = threadIdx.y, n_chunks = blockDim.y;
+  const int s = blockIdx.y, W = blockDim.x, c = blockIdx.x * W + threadIdx.x, j = threadIdx.y, n_chunks = blockDim.y;
   const int first = seq_starts[s], n_new = seq_starts[s + 1] - first;
   const int per = (n_new + n_chunks - 1) / n_chunks;
   const int lo = min(j * per, n_new), hi = min(lo + per, n_new);
   const bool live = c < width;
   float* A = sm;
-  float* B = sm + n_chunks * 32;
+  float* B = sm + n_chunks * W;
   if (n_chunks > 1) {
     float a_run = 1.f, b_run = 0.f;
     if (live) {
-#pragma unroll 4
-      for (int t = lo; t < hi; ++t) {
-        const float* row = zug + (int64_t)(first + t) * ld;
-        float z, cand;
-        gru_terms(row[off_z + c], row[off_u + c], z, cand);
-        a_run *= 1.f - z;
-        b_run = fmaf(z, cand, (1.f - z) * b_run);
+      for (int t0 = lo; t0 < hi; t0 += GRU_AHEAD) {          // the loads of GRU_AHEAD rows are in flight together
+        float a[GRU_AHEAD], u[GRU_AHEAD];
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+          const float* row = zug + (int64_t)(first + min(t0 + i, hi - 1)) * ld;
+          a[i] = row[off_z + c], u[i] = row[off_u + c];
+        }
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+          if (t0 + i >= hi) break;
+          float z, cand;
+          gru_terms(a[i], u[i], z, cand);
+          a_run *= 1.f - z;
+          b_run = fmaf(z, cand, (1.f - z) * b_run);
+        }
       }
     }
-    A[j * 32 + threadIdx.x] = a_run;
-    B[j * 32 + threadIdx.x] = b_run;
+    A[j * W + threadIdx.x] = a_run;
+    B[j * W + threadIdx.x] = b_run;
     __syncthreads();
   }
   if (!live) return;
   float* kept = state + (int64_t)seq_slots[s] * state_stride + state_off + c;
   float S = *kept;
-  for (int i = 0; i < j; ++i) S = fmaf(A[i * 32 + threadIdx.x], S, B[i * 32 + threadIdx.x]);
-#pragma unroll 4
-  for (int t = lo; t < hi; ++t) {
-    const float* row = zug + (int64_t)(first + t) * ld;
-    float z, cand;
-    gru_terms(row[off_z + c], row[off_u + c], z, cand);
-    S = fmaf(z, cand, (1.f - z) * S);
-    out[(int64_t)(first + t) * ld_out + c] = from_f32<T>(S * silu_f(row[off_g + c]));
+  for (int i = 0; i < j; ++i) S = fmaf(A[i * W + threadIdx.x], S, B[i * W + threadIdx.x]);
+  for (int t0 = lo; t0 < hi; t0 += GRU_AHEAD) {
+    float a[GRU_AHEAD], u[GRU_AHEAD], g[GRU_AHEAD];
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      const float* row = zug + (int64_t)(first + min(t0 + i, hi - 1)) * ld;
+      a[i] = row[off_z + c], u[i] = row[off_u + c], g[i] = row[off_g + c];
+    }
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      if (t0 + i >= hi) break;
+      float z, cand;
+      gru_terms(a[i], u[i], z, cand);
+      S = fmaf(z, cand, (1.f - z) * S);
+      out[(int64_t)(first + t0 + i) * ld_out + c] = from_f32<T>(S * silu_f(g[i]));
+    }
   }
   if (hi == n_new && (lo < hi || j == 0)) *kept = S;       // the chunk that holds the last row (an empty step: nothing changes)
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0, v = 0;
+    n = (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) ? v : 148;
+  }
+  return n;
 }
 
 }  // namespace
@@ -263,8 +290,10 @@ KVAD_EXPORT int kvad_min_gru(int out_dtype, const float* zug, int64_t ld, int of
   KVAD_REQUIRE(n_seqs >= 0 && width > 0 && n_chunks >= 1 && n_chunks <= 32 && zug && out && state, "min_gru: bad arguments");
   KVAD_REQUIRE(ld >= width && ld_out >= width && state_stride >= state_off + width, "min_gru: rows or state shorter than the width");
   if (n_seqs == 0) return KVAD_OK;
-  dim3 grid((width + 31) / 32, n_seqs), block(32, n_chunks);
-  const size_t smem = (size_t)2 * 32 * n_chunks * sizeof(float);
+  // 16 channels a block where 32 would leave SMs without one and the rows are walked in chunks (half a warp still reads whole sectors)
+  const int per_block = (n_chunks > 1 && (int64_t)((width + 31) / 32) * n_seqs < sm_count()) ? 16 : 32;
+  dim3 grid((width + per_block - 1) / per_block, n_seqs), block(per_block, n_chunks);
+  const size_t smem = (size_t)2 * per_block * n_chunks * sizeof(float);
   if (out_dtype == KVAD_DTYPE_F32)
     kvad_launch(min_gru_kernel<float>, grid, block, smem, stream, zug, ld, off_z, off_u, off_g, (float*)out, ld_out, state, state_stride,
                 state_off, seq_starts, seq_slots, width);

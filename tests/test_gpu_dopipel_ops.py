@@ -355,7 +355,7 @@ def gru_weights(n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n", [30, 48, 200])
+@pytest.mark.parametrize("n", [30, 48, 200, 1600])        # (1600 channels x 3 sequences: 32 channels a block; fewer: 16)
 def test_min_gru_whole_in_portions_and_row_by_row(dtype, n):
     rng, ops = np.random.default_rng(n), Ops(DT[dtype])
     lens, slots, W = [700, 9, 130], [3, 0, 5], gru_weights(n)
