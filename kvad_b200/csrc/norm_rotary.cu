@@ -163,7 +163,9 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, int64_t ld_a, const T* 
 // x += g * delta / rms(delta) on the 32-bit stream (g: one 32-bit number per column), then y = rmsnorm(x) with `w`
 // (y absent: only the sum).  With `write_back` (all rows are walked) the sum replaces x and delta is cleared; with a
 // row list nothing is written back.  Two sums of squares per row, each in column order through the same tree.
-template <typename TO>
+// IN_REGISTERS (few rows, up to 2048 columns): a row lies in its block's registers and every load is in flight before
+// the first sum; the sums run in the same order, so both forms give the same bits.
+template <typename TO, bool IN_REGISTERS>
 __global__ void __launch_bounds__(128)
 postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const float* __restrict__ g, float eps_post, int write_back,
                         const int* __restrict__ row_index, const void* __restrict__ w, int w_f32, int unit_offset,
@@ -175,6 +177,49 @@ postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const 
   const int64_t src = (int64_t)(row_index ? row_index[r] : r) * width;
   float* xr = x + src;
   float* dr = delta + src;
+  constexpr int PER = 16;
+  if (IN_REGISTERS) {
+    float d[PER], xv[PER], gg[PER], ww[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int c = threadIdx.x + 128 * k;
+      const bool in = c < width;
+      d[k] = in ? dr[c] : 0.f;
+      xv[k] = in ? xr[c] : 0.f;
+      gg[k] = in ? g[c] : 0.f;
+      ww[k] = (in && out != nullptr && w != nullptr) ? load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f) : 1.f;
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k)
+      if (threadIdx.x + 128 * k < width) sq = fmaf(d[k], d[k], sq);
+    sq = block_sum(sq, scratch);
+    const float inv_d = 1.0f / sqrtf(sq / (float)width + eps_post);
+    float sq_x = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int c = threadIdx.x + 128 * k;
+      if (c < width) {
+        const float v = fmaf(d[k] * inv_d, gg[k], xv[k]);
+        if (write_back) {
+          xr[c] = v;
+          dr[c] = 0.f;
+        }
+        sq_x = fmaf(v, v, sq_x);
+        xv[k] = v;
+      }
+    }
+    if (out == nullptr) return;
+    sq_x = block_sum(sq_x, scratch);
+    const float inv = 1.0f / sqrtf(sq_x / (float)width + eps);
+    TO* o = out + (int64_t)r * ld_out;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int c = threadIdx.x + 128 * k;
+      if (c < width) o[c] = from_f32<TO>(xv[k] * inv * ww[k]);
+    }
+    return;
+  }
   float sq = 0.f;
 #pragma unroll 4
   for (int c = threadIdx.x; c < width; c += 128) {
@@ -335,11 +380,18 @@ KVAD_EXPORT int kvad_postnorm_rmsnorm(int out_dtype, float* x, float* delta, con
   KVAD_REQUIRE(out == nullptr || ld_out >= width, "postnorm_rmsnorm: the output's rows are too short");
   if (n_rows == 0) return KVAD_OK;
   dim3 grid(n_rows), block(128);
-  if (out_dtype == KVAD_DTYPE_F32)
-    kvad_launch(postnorm_rmsnorm_kernel<float>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32, unit_offset,
+  const bool few = n_rows <= 4 * 148 && width <= 128 * 16;
+  if (out_dtype == KVAD_DTYPE_F32 && few)
+    kvad_launch(postnorm_rmsnorm_kernel<float, true>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32, unit_offset,
                 (float*)out, ld_out, width, eps);
+  else if (out_dtype == KVAD_DTYPE_F32)
+    kvad_launch(postnorm_rmsnorm_kernel<float, false>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32, unit_offset,
+                (float*)out, ld_out, width, eps);
+  else if (out_dtype == KVAD_DTYPE_BF16 && few)
+    kvad_launch(postnorm_rmsnorm_kernel<__nv_bfloat16, true>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32,
+                unit_offset, (__nv_bfloat16*)out, ld_out, width, eps);
   else if (out_dtype == KVAD_DTYPE_BF16)
-    kvad_launch(postnorm_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32,
+    kvad_launch(postnorm_rmsnorm_kernel<__nv_bfloat16, false>, grid, block, 0, stream, x, delta, g, eps_post, write_back, row_index, w, w_f32,
                 unit_offset, (__nv_bfloat16*)out, ld_out, width, eps);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "postnorm_rmsnorm: unknown dtype %d", out_dtype);

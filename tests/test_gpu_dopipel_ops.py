@@ -514,9 +514,9 @@ def test_mixture_with_identity_experts_and_a_gated_shared_expert(dtype, width, E
 
 # ----------------------------------------------------------------------------- the block's own steps
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [24, 54, 1000])
-def test_a_normed_sum_enters_the_stream_and_the_next_norm_reads_it(dtype, width):
-    rng, ops, n, eps_post, eps = np.random.default_rng(width), Ops(DT[dtype]), 37, 1e-5, 1e-6
+@pytest.mark.parametrize("width,n", [(24, 37), (54, 37), (1000, 37), (1000, 700), (2100, 5)])      # (few rows of up to 2048 columns lie in registers)
+def test_a_normed_sum_enters_the_stream_and_the_next_norm_reads_it(dtype, width, n):
+    rng, ops, eps_post, eps = np.random.default_rng(width), Ops(DT[dtype]), 1e-5, 1e-6
     x, delta = stored(rng.standard_normal((n, width)), "float32"), stored(rng.standard_normal((n, width)) * 3, "float32")
     gain, weight = stored(rng.standard_normal(width), "float32"), stored(rng.standard_normal(width), "bfloat16")
     new_x = x + pl.rms_norm(delta, gain, eps_post)
@@ -530,7 +530,7 @@ def test_a_normed_sum_enters_the_stream_and_the_next_norm_reads_it(dtype, width)
     ops.postnorm_rmsnorm(xs, ds, dev(gain, torch.float32), eps_post)
     assert rel(xs, new_x) < 3e-6 and float(ds.abs().max()) == 0.0
     # some rows only (the head's rows): the output alone, the stream and the sum stay
-    rows = [3, 36, 0]
+    rows = [3, n - 1, 0]
     xs, ds = dev(x, torch.float32), dev(delta, torch.float32)
     out = torch.zeros((3, width), device="cuda", dtype=DT[dtype])
     ops.postnorm_rmsnorm(xs, ds, dev(gain, torch.float32), eps_post, out, dev(weight, torch.bfloat16), eps, rows=i32(rows))
@@ -554,12 +554,13 @@ def test_the_stream_is_mixed_with_the_embedding_output(dtype, width, n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_squared_relu_alone_and_with_a_gate_per_row(dtype):
+@pytest.mark.parametrize("n,width,pad", [(33, 50, 0), (70, 64, 7), (300, 704, 7)])      # (rows in eights with a padded gate: 16-byte pieces in bfloat16)
+def test_squared_relu_alone_and_with_a_gate_per_row(dtype, n, width, pad):
     rng, ops = np.random.default_rng(5), Ops(DT[dtype])
-    x, g = stored(rng.standard_normal((33, 50)) * 2, dtype), stored(rng.standard_normal((33, 1)) * 2, dtype)
-    out = torch.zeros((33, 50), device="cuda", dtype=DT[dtype])
+    x, g = stored(rng.standard_normal((n, width)) * 2, dtype), stored(rng.standard_normal((n, 1)) * 2, dtype)
+    out = torch.zeros((n, width), device="cuda", dtype=DT[dtype])
     ops.relu_squared(dev(x, DT[dtype]), out)
     assert rel(out, np.maximum(x, 0) ** 2) < KTOL[dtype]
-    both = dev(np.concatenate([x, g], 1), DT[dtype])
-    ops.relu_squared(both[:, :50], out, row_gate=both[:, 50:])
+    both = dev(np.concatenate([x, g, np.zeros((n, pad))], 1), DT[dtype])
+    ops.relu_squared(both[:, :width], out, row_gate=both[:, width:width + 1])
     assert rel(out, np.maximum(x, 0) ** 2 * pl.sigmoid(g)) < KTOL[dtype]
