@@ -28,7 +28,7 @@ from .pages import PAGE_SIZE, SlotBook
 class KVView:
     """One cache entry's pages as a mixer sees them during a step."""
     k_pages: torch.Tensor          # [pages, kv heads, page size, head size]
-    v_pages: Optional[torch.Tensor]    # [pages, kv heads, page size, value size]; None: the group keeps no values
+    v_pages: Optional[torch.Tensor]    # [pages, value heads (the kv heads, or fewer), page size, value size]; None: the group keeps no values
     page_table: torch.Tensor       # int32 [sequences of the step, table width], this group's
     window: Optional[int]
     page_size: int
@@ -60,7 +60,8 @@ class DeviceCache:
             if isinstance(need, KVNeed):
                 shape = (len(group.entries), n_pages, need.n_kv_heads, page_size)
                 self.kv[g] = (torch.empty((*shape, need.head_dim), dtype=dtype, device=self.device),
-                              torch.empty((*shape, need.v_dim), dtype=dtype, device=self.device) if need.v_dim else None)
+                              torch.empty((len(group.entries), n_pages, need.v_heads, page_size, need.v_dim), dtype=dtype, device=self.device)
+                              if need.v_dim else None)
                 self._kv_group_index[g] = len(pages_per_group)
                 pages_per_group.append(n_pages)
                 windows.append(need.window)

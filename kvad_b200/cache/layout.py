@@ -22,6 +22,7 @@ class KVNeed:
     window: Optional[int] = None     # None: every position is kept
     value_dim: Optional[int] = None  # None: values are as long as keys; 0: no values are kept (they are read from the keys)
     keep_first: int = 0              # with a window: the first positions stay in reach of every later query
+    value_heads: Optional[int] = None  # None: as many value heads as key heads; else fewer (several key heads read one value head)
 
     def __post_init__(self):
         if self.n_kv_heads <= 0 or self.head_dim <= 0:
@@ -30,10 +31,16 @@ class KVNeed:
             raise ValueError("a window must be positive")
         if (self.value_dim is not None and self.value_dim < 0) or self.keep_first < 0:
             raise ValueError("value size and kept first positions cannot be negative")
+        if self.value_heads is not None and (self.value_heads <= 0 or self.n_kv_heads % self.value_heads):
+            raise ValueError("the key heads must divide evenly over the value heads")
 
     @property
     def v_dim(self) -> int:
         return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def v_heads(self) -> int:
+        return self.n_kv_heads if self.value_heads is None else self.value_heads
 
 
 @dataclass(frozen=True)
@@ -88,5 +95,5 @@ class CacheLayout:
         total = 0
         for g in self.groups:
             if isinstance(g.need, KVNeed):
-                total += len(g.entries) * g.need.n_kv_heads * (g.need.head_dim + g.need.v_dim) * element_size
+                total += len(g.entries) * (g.need.n_kv_heads * g.need.head_dim + g.need.v_heads * g.need.v_dim) * element_size
         return total

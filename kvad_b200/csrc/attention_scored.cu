@@ -23,6 +23,12 @@
 // with another layer's (`kv_store_blend`), queries, keys and values turned by their positions and the keys and values
 // stored in the same pass (`turn_store`), and a latent row normalised, its rotary part turned, and stored
 // (`latent_store`).
+//
+// Several key heads may share one value head (`key_maps` consecutive key heads read value head kvh / key_maps): the maps
+// of a differential attention are attentions of their own over the same values.  `diff_combine` then takes the second
+// map off the first, o = a1 - lambda a2, and makes each head a unit vector by its root mean square.  `norm_turn_store`
+// is `turn_store` for queries and keys that are RMS-normed first, head by head or over the whole projection, with a
+// factor on cosine and sine (stretched frequencies).
 #include "common.cuh"
 
 using namespace kvad;
@@ -40,6 +46,8 @@ struct ScoredArgs {
   int64_t k_page_stride, k_head_stride, v_page_stride, v_head_stride;   // in elements
   int ld_k, ld_v;                                                       // row strides inside a page
   int n_heads, n_kv_heads, dk, dv, hp, v_alias;
+  int key_maps;          // this many consecutive key heads read one value head
+  int out_f32;           // the output is 32-bit whatever the storage type (no gate then)
   float scale, softcap, slope_span;
   int window, keep_first;
   int vec_k, vec_v;      // keys / values can be fetched in 16-byte pieces
@@ -154,7 +162,7 @@ __global__ void __launch_bounds__(32 * NW) scored_attention_kernel(const ScoredA
     const int n_live = last_pos - key0 + 1;                             // keys of the tile that exist
     load_tile<T>(Ks, ldks, kt, a.ld_k, TK, dk, dkp, n_live, a.vec_k != 0, tid, THREADS);
     if (!a.v_alias) {
-      const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)kvh * a.v_head_stride + (int64_t)in_page * a.ld_v;
+      const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)(kvh / a.key_maps) * a.v_head_stride + (int64_t)in_page * a.ld_v;
       load_tile<T>(Vs, dv, vt, a.ld_v, TK, dv, dv, n_live, a.vec_v != 0, tid, THREADS);
     }
     __syncthreads();
@@ -260,7 +268,8 @@ __global__ void __launch_bounds__(32 * NW) scored_attention_kernel(const ScoredA
       if (d < dv) {
         float y = acc[r][i] * inv;
         if (gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(gate[grow * a.ld_gate + (int64_t)(h0 + hi) * dv + d])));
-        out[grow * a.ld_out + (int64_t)(h0 + hi) * dv + d] = from_f32<T>(y);
+        if (a.out_f32) reinterpret_cast<float*>(a.out)[grow * a.ld_out + (int64_t)(h0 + hi) * dv + d] = y;
+        else out[grow * a.ld_out + (int64_t)(h0 + hi) * dv + d] = from_f32<T>(y);
       }
     }
   }
@@ -270,7 +279,7 @@ __global__ void __launch_bounds__(32 * NW) scored_attention_kernel(const ScoredA
 // output entry; the parts are taken in split order, so the result does not depend on which block finished first.
 template <typename T>
 __global__ void scored_merge_kernel(const float* __restrict__ partial, int n_splits, int n_heads, int dv, T* __restrict__ out,
-                                    int64_t ld_out, const T* __restrict__ gate, int64_t ld_gate) {
+                                    int64_t ld_out, const T* __restrict__ gate, int64_t ld_gate, int out_f32) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x, h = blockIdx.y;
@@ -291,7 +300,8 @@ __global__ void scored_merge_kernel(const float* __restrict__ partial, int n_spl
     }
     y /= total;
     if (gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(gate[(int64_t)row * ld_gate + (int64_t)h * dv + d])));
-    out[(int64_t)row * ld_out + (int64_t)h * dv + d] = from_f32<T>(y);
+    if (out_f32) reinterpret_cast<float*>(out)[(int64_t)row * ld_out + (int64_t)h * dv + d] = y;
+    else out[(int64_t)row * ld_out + (int64_t)h * dv + d] = from_f32<T>(y);
   }
 }
 
@@ -310,7 +320,7 @@ int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cud
   KVAD_CHECK_LAUNCH("attention_scored");
   if (a.n_splits > 1) {       // (rows are single tokens here: row = sequence)
     kvad_launch(scored_merge_kernel<T>, dim3(n_seqs, a.n_heads), dim3(a.dv <= 64 ? 64 : 128), 0, stream, (const float*)a.partial, a.n_splits,
-                a.n_heads, a.dv, (T*)a.out, a.ld_out, (const T*)a.gate, a.ld_gate);
+                a.n_heads, a.dv, (T*)a.out, a.ld_out, (const T*)a.gate, a.ld_gate, a.out_f32);
     KVAD_CHECK_LAUNCH("attention_scored (merge)");
   }
   return KVAD_OK;
@@ -447,6 +457,105 @@ __global__ void turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __re
   }
 }
 
+// Queries and keys RMS-normed in 32-bit (over `span` consecutive entries of their row at a time: one head, or the whole
+// projection; weight entry (column % w_len), absent weights are ones), then the first `rot` entries of every head turned by
+// the row's position (pairs (i, i + rot/2); cosine and sine times `mscale`); queries are written back in place, keys
+// go to their pages, values (n_v heads of dv) are stored as they are.  A block per row; the row's queries and keys
+// lie in shared memory as 32-bit numbers while their sums of squares are taken, a warp per span.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src, int64_t ld_v,
+                       const void* __restrict__ wq, const void* __restrict__ wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k,
+                       float eps, const float* __restrict__ freq, int rot, float mscale, const int* __restrict__ row_seq,
+                       const int* __restrict__ row_pos, const int* __restrict__ page_table, int table_width, T* __restrict__ k_pages,
+                       T* __restrict__ v_pages, int n_heads, int n_kv, int n_v, int dk, int dv) {
+  extern __shared__ float nts[];
+  const int nq = n_heads * dk, nk = n_kv * dk, spans_q = span_q > 0 ? nq / span_q : 0, spans_k = span_k > 0 ? nk / span_k : 0;
+  float* xs = nts;                      // [nq + nk] the row's queries, then its keys
+  float* inv = nts + nq + nk;           // [spans_q + spans_k]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  const int pos = row_pos[r];
+  const int64_t page = page_table[(int64_t)row_seq[r] * table_width + pos / PAGE];
+  T* qr = q + (int64_t)r * ld_q;
+  const T* kr = k_src + (int64_t)r * ld_k;
+  for (int i = tid; i < nq + nk; i += blockDim.x) xs[i] = i < nq ? to_f32(qr[i]) : to_f32(kr[i - nq]);
+  __syncthreads();
+  for (int sp = warp; sp < spans_q + spans_k; sp += n_warps) {
+    const bool is_q = sp < spans_q;
+    const int len = is_q ? span_q : span_k;
+    const float* x = is_q ? xs + sp * span_q : xs + nq + (sp - spans_q) * span_k;
+    float sq = 0.f;
+    for (int c = lane; c < len; c += 32) sq = fmaf(x[c], x[c], sq);
+    sq = warp_sum(sq);
+    if (lane == 0) inv[sp] = 1.0f / sqrtf(sq / (float)len + eps);
+  }
+  __syncthreads();
+  const int half = rot / 2, per_head = half + (dk - rot);         // units of a head: pairs that turn, entries that pass
+  const int units = (n_heads + n_kv) * per_head;
+  for (int i = tid; i < units; i += blockDim.x) {
+    const int hd = i / per_head, p = i - hd * per_head;
+    const bool is_q = hd < n_heads;
+    const int col0 = hd * dk;                                      // the head's first column among [queries | keys]
+    const int own0 = is_q ? col0 : col0 - nq;                      // ... within its own projection
+    const void* w = is_q ? wq : wk;
+    const int wlen = is_q ? wlen_q : wlen_k, span = is_q ? span_q : span_k;
+    T* dst = is_q ? qr + own0 : k_pages + ((page * n_kv + (hd - n_heads)) * PAGE + pos % PAGE) * dk;
+    if (p < half) {
+      const int ea = p, eb = p + half;
+      float u = xs[col0 + ea], v = xs[col0 + eb];
+      if (span > 0) {
+        const float f = inv[(is_q ? 0 : spans_q) + own0 / span];   // (a head never straddles two spans)
+        u *= f * (w ? load_param(w, (own0 + ea) % wlen, w_f32) : 1.f);
+        v *= f * (w ? load_param(w, (own0 + eb) % wlen, w_f32) : 1.f);
+      }
+      float sn, cs;
+      sincosf((float)pos * freq[p], &sn, &cs);
+      sn *= mscale;
+      cs *= mscale;
+      dst[ea] = from_f32<T>(turn_first(u, v, cs, sn));
+      dst[eb] = from_f32<T>(turn_second(u, v, cs, sn));
+    } else {
+      const int e = rot + (p - half);
+      float u = xs[col0 + e];
+      if (span > 0) u *= inv[(is_q ? 0 : spans_q) + own0 / span] * (w ? load_param(w, (own0 + e) % wlen, w_f32) : 1.f);
+      dst[e] = from_f32<T>(u);
+    }
+  }
+  const T* vr = v_src + (int64_t)r * ld_v;
+  for (int i = tid; i < n_v * dv; i += blockDim.x) {
+    const int h = i / dv, d = i - h * dv;
+    v_pages[((page * n_v + h) * PAGE + pos % PAGE) * dv + d] = vr[i];
+  }
+}
+
+// Differential attention's last step.  `a` holds, per row, the maps' outputs in 32-bit, laid out [kv head][map][head of
+// the group][dv]; head h = kv * group + j of the output gets o = a1 - lambda a2, over sqrt(mean(o^2) + eps), times `gain`.
+// A warp per (row, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const float* __restrict__ a, int64_t ld_a, T* __restrict__ out, int64_t ld_out, int n_rows, int n_heads, int group, int dv,
+                    float lambda, float eps, float gain) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (int64_t)n_rows * n_heads) return;
+  const int64_t row = item / n_heads;
+  const int h = (int)(item % n_heads), kv = h / group, j = h - kv * group, lane = threadIdx.x & 31;
+  const float* a1 = a + row * ld_a + ((int64_t)(kv * 2) * group + j) * dv;
+  const float* a2 = a1 + (int64_t)group * dv;
+  float sq = 0.f;
+  for (int d = lane; d < dv; d += 32) {
+    const float o = fmaf(-lambda, a2[d], a1[d]);
+    sq = fmaf(o, o, sq);
+  }
+  sq = warp_sum(sq);
+  const float f = gain / sqrtf(sq / (float)dv + eps);
+  T* o_row = out + row * ld_out + (int64_t)h * dv;
+  for (int d = lane; d < dv; d += 32) o_row[d] = from_f32<T>(fmaf(-lambda, a2[d], a1[d]) * f);
+}
+
 // A warp per row: the first `rank` entries are RMS-normalised with a weight, the last `rot` entries turned by
 // the row's position (pairs interleaved or half apart), and the row goes to its place in pages of one head of
 // rank + rot entries.
@@ -566,7 +675,7 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
                                       int table_width, const void* k_pages, const void* v_pages, int n_seqs, int n_heads,
                                       int n_kv_heads, int dk, int dv, int page_size, int max_new, int hp, float scale,
                                       float softcap, float slope_span, int window, int keep_first, int n_splits, float* partial,
-                                      cudaStream_t stream) {
+                                      int key_maps, int out_f32, cudaStream_t stream) {
   KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && table_width > 0 && max_new >= 0,
                "attention (scored): bad sizes seqs=%d heads=%d kv_heads=%d dk=%d dv=%d", n_seqs, n_heads, n_kv_heads, dk, dv);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
@@ -579,15 +688,17 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   KVAD_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, "attention (scored): %d sequences x %d heads are more than one launch takes", n_seqs, n_heads);
   if (n_seqs == 0 || max_new == 0) return KVAD_OK;
   const bool alias = v_pages == k_pages;
+  KVAD_REQUIRE(key_maps >= 1 && n_kv_heads % key_maps == 0 && (key_maps == 1 || !alias), "attention (scored): %d key heads do not share values %d by %d", n_kv_heads, key_maps, key_maps);
+  KVAD_REQUIRE(!out_f32 || gate == nullptr, "attention (scored): a 32-bit output takes no gate");
   KVAD_REQUIRE(!alias || dv <= dk, "attention (scored): values read from the keys cannot be longer than a key");
   ScoredArgs a;
   a.q = q; a.ld_q = ld_q; a.out = out; a.ld_out = ld_out; a.gate = gate; a.ld_gate = ld_gate;
   a.seq_starts = seq_starts; a.kv_lens = kv_lens; a.page_table = page_table; a.table_width = table_width;
   a.k_pages = k_pages; a.v_pages = v_pages;
   a.ld_k = dk; a.k_head_stride = (int64_t)PAGE * dk; a.k_page_stride = (int64_t)n_kv_heads * PAGE * dk;
-  a.ld_v = alias ? dk : dv; a.v_head_stride = (int64_t)PAGE * a.ld_v; a.v_page_stride = (int64_t)n_kv_heads * PAGE * a.ld_v;
+  a.ld_v = alias ? dk : dv; a.v_head_stride = (int64_t)PAGE * a.ld_v; a.v_page_stride = (int64_t)(n_kv_heads / key_maps) * PAGE * a.ld_v;
   a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.dk = dk; a.dv = dv; a.hp = hp; a.v_alias = alias ? 1 : 0;
-  a.n_splits = n_splits; a.partial = partial;
+  a.n_splits = n_splits; a.partial = partial; a.key_maps = key_maps; a.out_f32 = out_f32 ? 1 : 0;
   const int piece = dtype == KVAD_DTYPE_F32 ? 4 : 8;
   a.vec_k = (dk % piece == 0 && (reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) ? 1 : 0;
   a.vec_v = (!alias && dv % piece == 0 && (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0) ? 1 : 0;
@@ -666,6 +777,61 @@ KVAD_EXPORT int kvad_latent_store(int dtype, const void* src, int64_t ld, const 
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "latent_store: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("latent_store");
+  return KVAD_OK;
+}
+
+// span_q / span_k: how many consecutive entries of the queries' / keys' projection are normed together (0: no norm; a
+// multiple of dk that divides the projection); wq / wk: the norms' weights (w_len entries each, float32 or bfloat16; null:
+// ones).  n_v: value heads (the pages of values have that many).  rot: entries of a head that turn (even, at most dk).
+KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const void* k_src, int64_t ld_k, const void* v_src, int64_t ld_v,
+                                     const void* wq, const void* wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k, float eps,
+                                     const float* freq, int rot, float mscale, const int* row_seq, const int* row_pos, const int* page_table,
+                                     int table_width, void* k_pages, void* v_pages, int n_rows, int n_heads, int n_kv, int n_v, int dk, int dv,
+                                     int page_size, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_kv > 0 && n_v > 0 && dk > 0 && dv > 0 && table_width > 0,
+               "norm_turn_store: bad sizes rows=%d heads=%d kv_heads=%d value heads=%d dk=%d dv=%d", n_rows, n_heads, n_kv, n_v, dk, dv);
+  KVAD_REQUIRE(page_size == PAGE, "norm_turn_store: pages of %d positions, not %d", PAGE, page_size);
+  KVAD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "norm_turn_store: %d of %d key entries cannot turn in pairs", rot, dk);
+  KVAD_REQUIRE(span_q >= 0 && span_k >= 0 && (span_q == 0 || (span_q % dk == 0 && (n_heads * dk) % span_q == 0)) &&
+               (span_k == 0 || (span_k % dk == 0 && (n_kv * dk) % span_k == 0)), "norm_turn_store: norms over %d and %d entries do not fit heads of %d", span_q, span_k, dk);
+  KVAD_REQUIRE((wq == nullptr || wlen_q > 0) && (wk == nullptr || wlen_k > 0), "norm_turn_store: a weight needs its length");
+  KVAD_REQUIRE(q && k_src && v_src && k_pages && v_pages, "norm_turn_store: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  const int nq = n_heads * dk, nk = n_kv * dk;
+  const size_t smem = ((size_t)nq + nk + (span_q ? nq / span_q : 0) + (span_k ? nk / span_k : 0)) * sizeof(float);
+  KVAD_REQUIRE(smem <= 200 * 1024, "norm_turn_store: rows of %d queries and keys do not fit shared memory", nq + nk);
+#define KVAD_NTS(T)                                                                                                                          \
+  do {                                                                                                                                       \
+    static size_t configured = 0;                                                                                                            \
+    if (smem > 48 * 1024 && smem > configured) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(norm_turn_store_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
+      if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "norm_turn_store: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+      configured = smem;                                                                                                                     \
+    }                                                                                                                                        \
+    kvad_launch(norm_turn_store_kernel<T>, dim3(n_rows), dim3(256), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, wq, wk, \
+                w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width, (T*)k_pages,       \
+                (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                                    \
+  } while (0)
+  if (dtype == KVAD_DTYPE_F32) KVAD_NTS(float);
+  else if (dtype == KVAD_DTYPE_BF16) KVAD_NTS(__nv_bfloat16);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "norm_turn_store: unknown dtype %d", dtype);
+#undef KVAD_NTS
+  KVAD_CHECK_LAUNCH("norm_turn_store");
+  return KVAD_OK;
+}
+
+// a: float32 [rows, 2 heads x dv] as the attention left it ([kv head][map][head of the group][dv]); out: [rows, heads x dv].
+KVAD_EXPORT int kvad_diff_combine(int dtype, const float* a, int64_t ld_a, void* out, int64_t ld_out, int n_rows, int n_heads, int group, int dv,
+                                  float lambda, float eps, float gain, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && group > 0 && n_heads % group == 0 && dv > 0 && a && out, "diff_combine: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t items = (int64_t)n_rows * n_heads;
+  dim3 grid((unsigned)((items + 3) / 4)), block(128);
+  if (dtype == KVAD_DTYPE_F32) kvad_launch(diff_combine_kernel<float>, grid, block, 0, stream, a, ld_a, (float*)out, ld_out, n_rows, n_heads, group, dv, lambda, eps, gain);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(diff_combine_kernel<__nv_bfloat16>, grid, block, 0, stream, a, ld_a, (__nv_bfloat16*)out, ld_out, n_rows, n_heads, group, dv, lambda, eps, gain);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "diff_combine: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("diff_combine");
   return KVAD_OK;
 }
 

@@ -80,6 +80,10 @@ __device__ __forceinline__ void route_row(const float* __restrict__ logits, int6
     mine[k] = at;
     wt[k] = best;
   }
+  if (mode == 2) {      // every chosen expert weighs in with the sigmoid of its own logit (the same order: the sigmoid rises)
+    for (int k = 0; k < top; ++k) wt[k] = 1.0f / (1.0f + expf(-wt[k]));
+    return;
+  }
   const float top_z = wt[0];
   float sum = 0.f;
   for (int k = 0; k < top; ++k) {
@@ -378,6 +382,31 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, con
   }
 }
 
+// out = act(s g) * (s u), s = scale[slot[p]] for position p (1 where `scale` is null or the position is padding):
+// an expert that reads its input times the router's weight, W (s h) = s (W h), so the weight is applied to the two
+// products' results instead of to their input.  act: 0 = silu, 3 = the tanh form of GELU.  32-bit arithmetic.
+template <typename T>
+__global__ void scaled_glu_kernel(const T* __restrict__ gate, int64_t ld_g, const T* __restrict__ up, int64_t ld_u, T* __restrict__ out,
+                                  int64_t ld_o, const int* __restrict__ slot, const float* __restrict__ scale, int n_rows, int width, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    float s = 1.f;
+    if (slot != nullptr) {
+      const int at = slot[r];
+      if (at < 0) {                       // (padding may hold anything)
+        out[r * ld_o + c] = from_f32<T>(0.f);
+        continue;
+      }
+      s = scale[at];
+    }
+    const float g = s * to_f32(gate[r * ld_g + c]), u = s * to_f32(up[r * ld_u + c]);
+    out[r * ld_o + c] = from_f32<T>((act == 0 ? g / (1.0f + expf(-g)) : gelu_tanh(g)) * u);
+  }
+}
+
 // out = max(x, 0)^2, times sigmoid(row_gate[r * ld_gate]) where a gate is given (one number per row).
 template <typename T>
 __global__ void relu_squared_kernel(const T* __restrict__ x, int64_t ld_x, T* __restrict__ out, int64_t ld_o, const T* __restrict__ row_gate,
@@ -432,7 +461,7 @@ __global__ void moe_combine_vec_kernel(float* __restrict__ residual, const float
     const int c = (int)(i - r * per_row) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top; ++k) {
-      const float wk = weight[r * top + k];
+      const float wk = weight ? weight[r * top + k] : 1.f;
       const int at = slot_pos[r * top + k];
       float4 v;
       if (at >= 0) v = *reinterpret_cast<const float4*>(outs + (int64_t)at * ld_outs + c);
@@ -458,7 +487,7 @@ __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
       const int at = slot_pos[r * top + k];
-      acc = fmaf(weight[r * top + k], at >= 0 ? outs[(int64_t)at * ld_outs + c] : to_f32(input[r * ld_in + c]), acc);
+      acc = fmaf(weight ? weight[r * top + k] : 1.f, at >= 0 ? outs[(int64_t)at * ld_outs + c] : to_f32(input[r * ld_in + c]), acc);
     }
     residual[i] += acc;
   }
@@ -488,7 +517,7 @@ KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int 
 KVAD_EXPORT int kvad_moe_sort(int* chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows, int* tile_expert,
                               int* pos_row, int* pos_slot, int* slot_pos, const float* logits, int64_t ld_logits, float* weight,
                               int mode, const float* correction, int n_real, cudaStream_t stream) {
-  KVAD_REQUIRE((mode == 0 || mode == 1) && n_real >= 0 && n_real <= n_experts, "moe_sort: bad routing mode or expert counts");
+  KVAD_REQUIRE((mode == 0 || mode == 1 || mode == 2) && n_real >= 0 && n_real <= n_experts, "moe_sort: bad routing mode or expert counts");
   KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096 && tile_rows > 0, "moe_sort: bad sizes");
   KVAD_REQUIRE(logits == nullptr || (weight != nullptr && top <= n_experts && ld_logits >= n_experts), "moe_sort: routing needs weights to write");
   KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_real, "moe_sort: %d tiles cannot hold %d slots of %d experts",
@@ -587,7 +616,7 @@ KVAD_EXPORT int kvad_gather_rows(int dtype, const void* a, int64_t ld_a, const i
 // input (of `in_dtype`, may be null where every slot has a position): the rows the experts read, for slots without a position.
 KVAD_EXPORT int kvad_moe_combine(float* residual, const float* outs, int64_t ld_outs, const int* slot_pos, const float* weight, int n_rows,
                                  int width, int top, int in_dtype, const void* input, int64_t ld_in, cudaStream_t stream) {
-  KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && outs && slot_pos && weight, "moe_combine: bad arguments");
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && outs && slot_pos, "moe_combine: bad arguments");
   if (n_rows == 0) return KVAD_OK;
   const bool vec = width % 4 == 0 && ld_outs % 4 == 0 && ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(outs)) & 15) == 0;
   dim3 grid(vec ? flat_blocks((int64_t)n_rows * (width / 4), 256) : flat_blocks((int64_t)n_rows * width, 256)), block(256);
@@ -626,6 +655,25 @@ KVAD_EXPORT int kvad_relu_squared(int dtype, const void* x, int64_t ld_x, void* 
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "relu_squared: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("relu_squared");
+  return KVAD_OK;
+}
+
+// slot: for every row of gate / up the (row, choice) pair it stands for (-1: padding, whose output is zero), scale: one
+// float32 per pair; both null: no scaling.
+KVAD_EXPORT int kvad_scaled_glu(int dtype, const void* gate, int64_t ld_g, const void* up, int64_t ld_u, void* out, int64_t ld_o, const int* slot,
+                                const float* scale, int n_rows, int width, int act, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && gate && up && out && (act == 0 || act == 3) && ((slot == nullptr) == (scale == nullptr)),
+               "scaled_glu: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(scaled_glu_kernel<float>, grid, block, 0, stream, (const float*)gate, ld_g, (const float*)up, ld_u, (float*)out, ld_o, slot, scale,
+                n_rows, width, act);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(scaled_glu_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)gate, ld_g, (const __nv_bfloat16*)up, ld_u,
+                (__nv_bfloat16*)out, ld_o, slot, scale, n_rows, width, act);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "scaled_glu: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("scaled_glu");
   return KVAD_OK;
 }
 

@@ -9,12 +9,17 @@
 //                     entry i with i + dims/2 ("half") or 2i with 2i + 1 ("interleaved")
 //                     (`inverse`: by the negative angle; `head_gate`: each head's turned entries times the sigmoid
 //                     of one number per row and head)
-//   gate_mul          out = act(a) * b,  act = silu, sigmoid or relu
+//   gate_mul          out = act(a) * b,  act = silu, sigmoid, relu or the tanh form of GELU
 //   scale_add         x += mult * delta; delta = 0
 //   postnorm_rmsnorm  x += g * delta / rms(delta); delta = 0; y = rmsnorm(x)   - a block that norms a sublayer's result
 //                     before it scales it into the stream leaves that to the next reader of the stream (y may be absent)
 //   head_gate         x[r, h, :] *= sigmoid(gate[r, h])
 //   stream_concat     out = [x | x0] in the compute dtype: two 32-bit streams side by side as one product's input
+//   cast_rows         y = x in the compute dtype: what a sublayer that reads the stream itself multiplies with
+//                     (postnorm_rmsnorm with a negative eps leaves the same beside the sum it takes up)
+//   pair_norm_sum     delta += mult * (ga * a / rms(a) + gb * b / rms(b)); a = 0; b = 0   - two mixers side by side,
+//                     each normed over the model width before they are averaged
+//   tanh_cap          x = cap * tanh(x / cap) in place (32-bit logits)
 #include "common.cuh"
 
 using namespace kvad;
@@ -156,13 +161,14 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, int64_t ld_a, const T* 
     const int r = (int)(i / width), c = (int)(i % width);
     const float g = to_f32(a[(int64_t)r * ld_a + c]);
     const float v = to_f32(b[(int64_t)r * ld_b + c]);
-    out[(int64_t)r * ld_out + c] = from_f32<T>((act == 0 ? silu_f(g) : act == 1 ? sigmoid_f(g) : fmaxf(g, 0.f)) * v);
+    out[(int64_t)r * ld_out + c] = from_f32<T>((act == 0 ? silu_f(g) : act == 1 ? sigmoid_f(g) : act == 2 ? fmaxf(g, 0.f) : gelu_tanh(g)) * v);
   }
 }
 
 // x += g * delta / rms(delta) on the 32-bit stream (g: one 32-bit number per column), then y = rmsnorm(x) with `w`
 // (y absent: only the sum).  With `write_back` (all rows are walked) the sum replaces x and delta is cleared; with a
 // row list nothing is written back.  Two sums of squares per row, each in column order through the same tree.
+// A negative `eps`: y = x as it is (no norm, no weight) - for a reader that wants the stream itself in its own dtype.
 // IN_REGISTERS (few rows, up to 2048 columns): a row lies in its block's registers and every load is in flight before
 // the first sum; the sums run in the same order, so both forms give the same bits.
 template <typename TO, bool IN_REGISTERS>
@@ -211,7 +217,7 @@ postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const 
     }
     if (out == nullptr) return;
     sq_x = block_sum(sq_x, scratch);
-    const float inv = 1.0f / sqrtf(sq_x / (float)width + eps);
+    const float inv = eps < 0.f ? 1.f : 1.0f / sqrtf(sq_x / (float)width + eps);
     TO* o = out + (int64_t)r * ld_out;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
@@ -240,7 +246,7 @@ postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const 
   }
   if (out == nullptr) return;
   sq_x = block_sum(sq_x, scratch);
-  const float inv = 1.0f / sqrtf(sq_x / (float)width + eps);
+  const float inv = eps < 0.f ? 1.f : 1.0f / sqrtf(sq_x / (float)width + eps);
   TO* o = out + (int64_t)r * ld_out;
 #pragma unroll 4
   for (int c = threadIdx.x; c < width; c += 128) {
@@ -249,6 +255,56 @@ postnorm_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, const 
     if (w != nullptr) gain = load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f);
     o[c] = from_f32<TO>(v * inv * gain);
   }
+}
+
+// y = x in the compute dtype (rows of the 32-bit stream, all of them or those a list names).
+template <typename TO>
+__global__ void cast_rows_kernel(const float* __restrict__ x, const int* __restrict__ row_index, TO* __restrict__ out, int64_t ld_out,
+                                 int n_rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    out[r * ld_out + c] = from_f32<TO>(x[(int64_t)(row_index ? row_index[r] : r) * width + c]);
+  }
+}
+
+// delta += mult * (ga * a / rms(a) + gb * b / rms(b)); a = 0; b = 0 (all 32-bit, rows of `width`; ga, gb one number per
+// column).  A block per row; the two sums of squares run in column order through the same tree.
+__global__ void __launch_bounds__(128)
+pair_norm_sum_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ ga, const float* __restrict__ gb,
+                     float* __restrict__ delta, int width, float eps, float mult) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  float* ar = a + (int64_t)blockIdx.x * width;
+  float* br = b + (int64_t)blockIdx.x * width;
+  float* dr = delta + (int64_t)blockIdx.x * width;
+  float sa = 0.f, sb = 0.f;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    const float u = ar[c], v = br[c];
+    sa = fmaf(u, u, sa);
+    sb = fmaf(v, v, sb);
+  }
+  sa = block_sum(sa, scratch);
+  sb = block_sum(sb, scratch);
+  const float ia = 1.0f / sqrtf(sa / (float)width + eps), ib = 1.0f / sqrtf(sb / (float)width + eps);
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    const float u = ar[c] * ia * ga[c], v = br[c] * ib * gb[c];
+    dr[c] = fmaf(mult, u + v, dr[c]);
+    ar[c] = 0.f;
+    br[c] = 0.f;
+  }
+}
+
+__global__ void tanh_cap_kernel(float* __restrict__ x, int64_t total, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
 }
 
 // x[r, h * dv + d] *= sigmoid(gate[r, h]): one number per row and head.
@@ -354,10 +410,10 @@ KVAD_EXPORT int kvad_rotary(int dtype, const void* src, int64_t ld_src, int head
   return KVAD_OK;
 }
 
-// act: 0 = silu, 1 = sigmoid, 2 = relu.
+// act: 0 = silu, 1 = sigmoid, 2 = relu, 3 = the tanh form of GELU.
 KVAD_EXPORT int kvad_gate_mul(int dtype, const void* a, int64_t ld_a, const void* b, int64_t ld_b, void* out, int64_t ld_out,
                               int n_rows, int width, int act, cudaStream_t stream) {
-  KVAD_REQUIRE(n_rows >= 0 && width > 0 && act >= 0 && act <= 2, "gate_mul: bad arguments rows=%d width=%d act=%d", n_rows, width, act);
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && act >= 0 && act <= 3, "gate_mul: bad arguments rows=%d width=%d act=%d", n_rows, width, act);
   if (n_rows == 0) return KVAD_OK;
   dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
   if (dtype == KVAD_DTYPE_F32)
@@ -420,6 +476,37 @@ KVAD_EXPORT int kvad_stream_concat(int dtype, const float* x, const float* x0, v
   else if (dtype == KVAD_DTYPE_BF16) kvad_launch(stream_concat_kernel<__nv_bfloat16>, grid, block, 0, stream, x, x0, (__nv_bfloat16*)out, n_rows, width);
   else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "stream_concat: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("stream_concat");
+  return KVAD_OK;
+}
+
+// rows: a list of stream rows (n_rows of them) or null (the first n_rows).
+KVAD_EXPORT int kvad_cast_rows(int out_dtype, const float* x, const int* row_index, void* out, int64_t ld_out, int n_rows, int width,
+                               cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && x && out && ld_out >= width, "cast_rows: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (out_dtype == KVAD_DTYPE_F32) kvad_launch(cast_rows_kernel<float>, grid, block, 0, stream, x, row_index, (float*)out, ld_out, n_rows, width);
+  else if (out_dtype == KVAD_DTYPE_BF16)
+    kvad_launch(cast_rows_kernel<__nv_bfloat16>, grid, block, 0, stream, x, row_index, (__nv_bfloat16*)out, ld_out, n_rows, width);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "cast_rows: unknown dtype %d", out_dtype);
+  KVAD_CHECK_LAUNCH("cast_rows");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_pair_norm_sum(float* a, float* b, const float* ga, const float* gb, float* delta, int n_rows, int width, float eps,
+                                   float mult, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && a && b && ga && gb && delta, "pair_norm_sum: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  kvad_launch(pair_norm_sum_kernel, dim3(n_rows), dim3(128), 0, stream, a, b, ga, gb, delta, width, eps, mult);
+  KVAD_CHECK_LAUNCH("pair_norm_sum");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_tanh_cap(float* x, int64_t total, float cap, cudaStream_t stream) {
+  KVAD_REQUIRE(total >= 0 && x && cap > 0.f, "tanh_cap: bad arguments");
+  if (total == 0) return KVAD_OK;
+  kvad_launch(tanh_cap_kernel, dim3(flat_blocks(total, 256)), dim3(256), 0, stream, x, total, cap);
+  KVAD_CHECK_LAUNCH("tanh_cap");
   return KVAD_OK;
 }
 

@@ -6,7 +6,9 @@
 // with q and k turned by the row's position first (rotary, pairs half apart or interleaved, over the first
 // `rot_dims` entries; angles, sines and the turned values in 32-bit), k scaled by `k_scale` after turning,
 // and the output optionally divided by its root mean square per head and multiplied by silu(gate) where it
-// is written.  Everything after the projections runs in 32-bit.
+// is written.  Everything after the projections runs in 32-bit.  With `act` q, k and v pass a silu where they are
+// staged (linear attention behind silu), and with `finish` off the raw 32-bit read-outs are all the kernel leaves:
+// `row_norm_gate` then norms all heads of a row together, with a weight, times sigmoid(gate).
 //
 // A block owns one (sequence, head, range of value columns) - the columns of the state are independent of one
 // another - and walks the sequence's rows of this step in order, 16 at a time: the block turns and stages the 16
@@ -38,6 +40,8 @@ struct RetentionArgs {
   int heads, dk, dv, split, vc, fused, vec;
   float k_scale, eps;
   int unit_norm;
+  int act;                              // 1: q, k and v pass a silu as they are staged
+  int finish;                           // 0: only the raw 32-bit read-outs are written (to `raw`)
 };
 
 __device__ __forceinline__ void unpack16(const uint4& raw, float* f, float) {
@@ -52,6 +56,8 @@ __device__ __forceinline__ void unpack16(const uint4& raw, float* f, __nv_bfloat
     f[2 * t + 1] = v.y;
   }
 }
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
 template <typename T>
 __device__ __forceinline__ void finish_row(const float* o, int dv, int lane, bool unit_norm, float eps, const T* gate, T* out) {
@@ -142,6 +148,13 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
           float fq[E], fk[E];
           unpack16(q_pf[u], fq, T());
           unpack16(k_pf[u], fk, T());
+          if (a.act) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              fq[e] = c + e < dk ? silu_f(fq[e]) : 0.f;
+              fk[e] = c + e < dk ? silu_f(fk[e]) : 0.f;
+            }
+          }
 #pragma unroll
           for (int e = 0; e < E; ++e) fk[e] *= (c + e < 2 * half ? 1.f : a.k_scale);      // (turned entries are scaled after turning)
           float* qd = qs + t * lds + (c / DPT) * SEG + c % DPT;
@@ -156,6 +169,10 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
       if (tid < nb * vpr) {
         float fv[E];
         unpack16(v_pf, fv, T());
+        if (a.act) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) fv[e] = silu_f(fv[e]);
+        }
 #pragma unroll
         for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(vs + tid * E + e) = make_float4(fv[e], fv[e + 1], fv[e + 2], fv[e + 3]);
       }
@@ -165,13 +182,20 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
       for (int i = tid; i < nb * dkp; i += nthreads) {
         const int t = i / dkp, d = i - t * dkp, at = t * lds + (d / DPT) * SEG + d % DPT;
         const int64_t row = start + t0 + t;
-        qs[at] = d < dk ? to_f32(q[row * a.ld_q + (int64_t)h * dk + d]) : 0.f;
-        ks[at] = d < dk ? to_f32(k[row * a.ld_k + (int64_t)h * dk + d]) * (d < 2 * half ? 1.f : a.k_scale) : 0.f;
+        float qv = d < dk ? to_f32(q[row * a.ld_q + (int64_t)h * dk + d]) : 0.f;
+        float kv = d < dk ? to_f32(k[row * a.ld_k + (int64_t)h * dk + d]) : 0.f;
+        if (a.act) {
+          qv = silu_f(qv);
+          kv = silu_f(kv);
+        }
+        qs[at] = qv;
+        ks[at] = kv * (d < 2 * half ? 1.f : a.k_scale);
       }
 #pragma unroll 4
       for (int i = tid; i < nb * vc; i += nthreads) {
         const int t = i / vc, c = i - t * vc;
-        vs[i] = v_base + c < dv ? to_f32(v[(int64_t)(start + t0 + t) * a.ld_v + (int64_t)h * dv + v_base + c]) : 0.f;
+        float vv = v_base + c < dv ? to_f32(v[(int64_t)(start + t0 + t) * a.ld_v + (int64_t)h * dv + v_base + c]) : 0.f;
+        vs[i] = a.act ? silu_f(vv) : vv;
       }
     }
     if (half > 0) {
@@ -276,6 +300,29 @@ retention_finish_kernel(const float* __restrict__ raw, int n_rows, int heads, in
                 gate ? gate + row * ld_gate + (int64_t)h * dv : nullptr, out + row * ld_out + (int64_t)h * dv);
 }
 
+// out = raw / sqrt(mean over the whole row (raw^2) + eps) * w * sigmoid(gate): a block per row of 32-bit read-outs.
+template <typename T>
+__global__ void __launch_bounds__(128)
+row_norm_gate_kernel(const float* __restrict__ raw, int64_t ld_raw, const T* __restrict__ gate, int64_t ld_gate, const void* __restrict__ w,
+                     int w_f32, T* __restrict__ out, int64_t ld_out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* o = raw + (int64_t)blockIdx.x * ld_raw;
+  float sq = 0.f;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) sq = fmaf(o[c], o[c], sq);
+  sq = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(sq / (float)width + eps);
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
+    float y = o[c] * inv;
+    if (w != nullptr) y *= load_param(w, c, w_f32);
+    if (gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(gate[(int64_t)blockIdx.x * ld_gate + c])));
+    out[(int64_t)blockIdx.x * ld_out + c] = from_f32<T>(y);
+  }
+}
+
 // How the state of a head is spread: a thread holds DPT key entries of two columns - 8 of them, so that the walk
 // over a row is short (a head of 128 key entries: 16 lanes a column pair), more only where 32 lanes are not enough -
 // and the threads that carry state are at most 128 a block and hold at most 32 columns (more blocks rather than
@@ -306,7 +353,7 @@ int launch_retention(const RetentionArgs& a, int n_seqs, int n_rows, cudaStream_
   const int threads = n_rows > n_seqs ? 256 : ((a.vc / VPT) * a.split + 31) / 32 * 32;
   kvad_launch(retention_kernel<T, DPT>, dim3(n_seqs, a.heads, (a.dv + a.vc - 1) / a.vc), dim3(threads), smem, stream, a);
   KVAD_CHECK_LAUNCH("retention");
-  if (!a.fused) {
+  if (!a.fused && a.finish) {
     const int64_t items = (int64_t)n_rows * a.heads;
     kvad_launch(retention_finish_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)a.raw, n_rows, a.heads, a.dv,
                 a.unit_norm, a.eps, (const T*)a.gate, a.ld_gate, (T*)a.out, a.ld_out);
@@ -319,7 +366,7 @@ template <typename T>
 int dispatch_retention(RetentionArgs& a, int n_seqs, int n_rows, cudaStream_t stream) {
   const Spread z = spread_of(a.dk, a.dv);
   if (z.dpt > 32) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "retention: keys of %d entries a head are above this kernel's limit of 1024", a.dk);
-  a.split = z.split; a.vc = z.vc; a.fused = z.fused;
+  a.split = z.split; a.vc = z.vc; a.fused = a.finish ? z.fused : 0;
   const int piece = 16 / (int)sizeof(T);                        // entries of a 16-byte piece
   a.vec = (a.dk % piece == 0 && a.dv % piece == 0 && a.vc % piece == 0 && a.ld_q % piece == 0 && a.ld_k % piece == 0 && a.ld_v % piece == 0 &&
            ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0) ? 1 : 0;
@@ -341,7 +388,7 @@ KVAD_EXPORT int kvad_retention(int dtype, const void* q, int64_t ld_q, const voi
                                const void* gate, int64_t ld_gate, void* out, int64_t ld_out, float* raw, int n_rows, float* state, const int* seq_starts,
                                const int* kv_lens, const int* seq_slots, const float* decay, const float* inv_freq, int rot_dims,
                                int interleaved, int n_seqs, int heads, int dk, int dv, float k_scale, float eps, int unit_norm,
-                               cudaStream_t stream) {
+                               int act, int finish, cudaStream_t stream) {
   KVAD_REQUIRE(n_seqs >= 0 && heads > 0 && dk > 0 && dv > 0, "retention: bad sizes seqs=%d heads=%d dk=%d dv=%d", n_seqs, heads, dk, dv);
   KVAD_REQUIRE(state != nullptr && decay != nullptr && seq_starts && kv_lens && seq_slots, "retention: needs state, decays and the step's sequences");
   KVAD_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, "retention: %d rotated entries of %d", rot_dims, dk);
@@ -351,10 +398,26 @@ KVAD_EXPORT int kvad_retention(int dtype, const void* q, int64_t ld_q, const voi
   a.q = q; a.k = k; a.v = v; a.gate = gate; a.ld_q = ld_q; a.ld_k = ld_k; a.ld_v = ld_v; a.ld_gate = ld_gate;
   a.out = out; a.ld_out = ld_out; a.raw = raw; a.vc = 0; a.fused = 1; a.vec = 0; a.state = state; a.seq_starts = seq_starts; a.kv_lens = kv_lens; a.seq_slots = seq_slots;
   a.decay = decay; a.inv_freq = rot_dims > 0 ? inv_freq : nullptr; a.rot_dims = rot_dims; a.interleaved = interleaved;
-  a.heads = heads; a.dk = dk; a.dv = dv; a.split = 1; a.k_scale = k_scale; a.eps = eps; a.unit_norm = unit_norm;
+  a.heads = heads; a.dk = dk; a.dv = dv; a.split = 1; a.k_scale = k_scale; a.eps = eps; a.unit_norm = unit_norm; a.act = act ? 1 : 0; a.finish = finish ? 1 : 0;
+  KVAD_REQUIRE(finish || raw != nullptr, "retention: raw read-outs need the 32-bit scratch");
   if (dtype == KVAD_DTYPE_F32) return dispatch_retention<float>(a, n_seqs, n_rows, stream);
   if (dtype == KVAD_DTYPE_BF16) return dispatch_retention<__nv_bfloat16>(a, n_seqs, n_rows, stream);
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "retention: unknown dtype %d", dtype);
+}
+
+// raw: float32 [rows, width]; gate, out: of `dtype`; w: `width` weights (float32 or bfloat16) or null.
+KVAD_EXPORT int kvad_row_norm_gate(int dtype, const float* raw, int64_t ld_raw, const void* gate, int64_t ld_gate, const void* w, int w_f32,
+                                   void* out, int64_t ld_out, int n_rows, int width, float eps, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && raw && out, "row_norm_gate: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(row_norm_gate_kernel<float>, dim3(n_rows), dim3(128), 0, stream, raw, ld_raw, (const float*)gate, ld_gate, w, w_f32, (float*)out, ld_out, width, eps);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(row_norm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, stream, raw, ld_raw, (const __nv_bfloat16*)gate, ld_gate, w, w_f32,
+                (__nv_bfloat16*)out, ld_out, width, eps);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "row_norm_gate: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("row_norm_gate");
+  return KVAD_OK;
 }
 
 KVAD_DEFINE_LAST_ERROR()

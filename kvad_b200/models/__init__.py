@@ -1,5 +1,5 @@
 """Architectures this build runs.  Importing a module registers it."""
 from .plan import LayerCall, Model, ModelPlan
-from . import gpt2, nifulix, vepinex, dopipel  # noqa: F401
+from . import gpt2, nifulix, vepinex, dopipel, dorevik  # noqa: F401
 
-__all__ = ["LayerCall", "Model", "ModelPlan", "gpt2", "nifulix", "vepinex", "dopipel"]
+__all__ = ["LayerCall", "Model", "ModelPlan", "gpt2", "nifulix", "vepinex", "dopipel", "dorevik"]

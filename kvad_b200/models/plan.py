@@ -84,6 +84,13 @@ class Model:
                 written[call.aux] = True
             if block.mixer is None:
                 continue
+            extra = getattr(block.mixer, "extra_cache_need", None)
+            extra = extra() if extra is not None else None
+            if extra is not None:      # a mixer of two mixers: the second one's need goes to the call's `aux` entry
+                if call.aux is None or call.aux == call.cache or needs[call.aux] is not None:
+                    raise ValueError(f"block {call.layer}'s mixer keeps two things: its call needs a cache entry `aux` that no other call uses")
+                needs[call.aux] = extra
+                written[call.aux] = True
             need = block.mixer.cache_need()
             if needs[call.cache] is not None and needs[call.cache] != need:
                 raise ValueError(f"cache entry {call.cache} is used by mixers with different needs")

@@ -95,11 +95,18 @@ _SIGNATURES = {
         "kvad_head_gate": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
         "kvad_stream_concat": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "kvad_gate_mul": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
+        "kvad_cast_rows": [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+        "kvad_pair_norm_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+        "kvad_tanh_cap": [c_void_p, c_int64, c_float, c_void_p],
     },
     "attention_scored": {
         "kvad_attention_scored": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+        "kvad_norm_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_int, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_diff_combine": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
         "kvad_kv_store_blend": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
@@ -111,8 +118,9 @@ _SIGNATURES = {
     "retention": {
         "kvad_retention": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                            c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                           c_int, c_float, c_float, c_int, c_void_p],
+                           c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
         "kvad_retention_needs_raw": [c_int, c_int],
+        "kvad_row_norm_gate": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float, c_void_p],
     },
     "gated_recurrence": {
         "kvad_gated_recurrence": [c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
@@ -137,6 +145,7 @@ _SIGNATURES = {
         "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_void_p],
         "kvad_clamped_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p],
+        "kvad_scaled_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "kvad_moe_combine": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     },
     "channel_recurrence": {
@@ -733,11 +742,16 @@ class Ops:
                              _ptr(head_gate), ld_g, _stream()), h)
 
     def postnorm_rmsnorm(self, x, delta, gain, eps_post: float, out=None, weight=None, eps: float = 0.0, *, unit_offset: bool = False,
-                         rows=None) -> None:
+                         rows=None, plain_out: bool = False) -> None:
         """x += gain * delta / sqrt(mean(delta^2) + eps_post) per row of the 32-bit stream (`gain`: float32, one per column),
         and, where `out` is given, out = rmsnorm(x) with `weight` and `eps`.  With all rows walked (`rows` None) the sum
-        replaces x and delta is cleared; with a row list only `out` is written."""
+        replaces x and delta is cleared; with a row list only `out` is written.  `plain_out`: out = x as it is, in out's
+        dtype (no norm, no weight) - for a sublayer that reads the stream itself."""
         _need_cuda(x, delta, gain, out, weight, rows)
+        if plain_out:
+            if weight is not None or out is None:
+                raise KernelError("postnorm_rmsnorm: a plain output has no weight")
+            eps = -1.0
         width = x.shape[1]
         if (x.dtype != torch.float32 or delta.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous()
                 or gain.dtype != torch.float32 or gain.numel() != width):
@@ -780,7 +794,37 @@ class Ops:
         h = lib("norm_rotary")
         _check(h.kvad_stream_concat(self.code, _ptr(x), _ptr(x0), _ptr(out), n, width, _stream()), h)
 
-    GATES = {"silu": 0, "sigmoid": 1, "relu": 2}
+    def cast_rows(self, x, out, rows=None) -> None:
+        """out = x in out's dtype: rows of the contiguous float32 stream (`rows`: an int32 list of them, else the first ones)."""
+        _need_cuda(x, out, rows)
+        n, width = out.shape
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[1] != width or (rows is None and x.shape[0] < n):
+            raise KernelError("cast_rows: rows of the contiguous float32 stream, as wide as the output")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n):
+            raise KernelError("cast_rows: row list must be int32, one per output row")
+        h = lib("norm_rotary")
+        _check(h.kvad_cast_rows(_code(out.dtype), _ptr(x), _ptr(rows), _ptr(out), _rows_view(out, "cast_rows output"), n, width, _stream()), h)
+
+    def pair_norm_sum(self, a, b, gain_a, gain_b, delta, eps: float, mult: float = 0.5) -> None:
+        """delta += mult * (gain_a * a / rms(a) + gain_b * b / rms(b)) row by row; a = 0; b = 0.  All float32 and contiguous,
+        one shape; the gains one number per column."""
+        _need_cuda(a, b, gain_a, gain_b, delta)
+        n, width = delta.shape
+        if (any(t.dtype != torch.float32 or not t.is_contiguous() for t in (a, b, gain_a, gain_b, delta)) or a.shape != delta.shape
+                or b.shape != delta.shape or gain_a.numel() != width or gain_b.numel() != width):
+            raise KernelError("pair_norm_sum: three contiguous float32 tensors of one shape and two float32 gains per column")
+        h = lib("norm_rotary")
+        _check(h.kvad_pair_norm_sum(_ptr(a), _ptr(b), _ptr(gain_a), _ptr(gain_b), _ptr(delta), n, width, float(eps), float(mult), _stream()), h)
+
+    def tanh_cap(self, x, cap: float) -> None:
+        """x = cap * tanh(x / cap) in place (contiguous float32)."""
+        _need_cuda(x)
+        if x.dtype != torch.float32 or not x.is_contiguous() or not cap > 0:
+            raise KernelError("tanh_cap: a contiguous float32 tensor and a positive cap")
+        h = lib("norm_rotary")
+        _check(h.kvad_tanh_cap(_ptr(x), x.numel(), float(cap), _stream()), h)
+
+    GATES = {"silu": 0, "sigmoid": 1, "relu": 2, "gelu_tanh": 3}
 
     def gate_mul(self, gate, value, out, act: str = "silu") -> None:
         """out = act(gate) * value, element by element (`gate`, `value`: views of equal shape, 32-bit arithmetic)."""
@@ -842,6 +886,52 @@ class Ops:
                                  _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), n, int(n_heads), n_kv, dk, dv, page,
                                  _stream()), h)
 
+    def norm_turn_store(self, q, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, *, q_weight=None, k_weight=None,
+                        span_q: int = 0, span_k: int = 0, eps: float = 0.0, inv_freq=None, dims: int = 0, mscale: float = 1.0) -> None:
+        """One pass over a step's rows: queries and keys RMS-normed in 32-bit over `span_q` / `span_k` consecutive entries of
+        their projection at a time (a head's size: head by head; the projection's: all heads at once; 0: no norm) with weights
+        as long as a span, then the first `dims` entries of every head turned by the row's position (pairs (i, i + dims/2),
+        cosine and sine times `mscale`); queries in place, keys on their way into the pages, values stored as they are.  The
+        values' pages may have fewer heads than the keys' (several key heads to one value head)."""
+        _need_cuda(q, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, q_weight, k_weight, inv_freq)
+        ld_q, ld_k, ld_v = _rows_view(q, "queries"), _rows_view(k_src, "keys"), _rows_view(v_src, "values")
+        _, n_kv, page, dk = k_pages.shape
+        n_v, dv, n = v_pages.shape[1], v_pages.shape[3], q.shape[0]
+        if (q.shape[1] != n_heads * dk or k_src.shape != (n, n_kv * dk) or v_src.shape != (n, n_v * dv) or v_pages.shape[0] != k_pages.shape[0]
+                or v_pages.shape[2] != page or {q.dtype, k_src.dtype, v_src.dtype, k_pages.dtype, v_pages.dtype} != {self.dtype}
+                or not k_pages.is_contiguous() or not v_pages.is_contiguous()):
+            raise KernelError(f"norm_turn_store: rows must match the cache's heads and be {self.dtype}")
+        if dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < dims // 2 or dims % 2 or dims > dk):
+            raise KernelError("norm_turn_store: an even number of a key's entries turns, with a float32 frequency per pair")
+        w_f32 = 1
+        for w, span in ((q_weight, span_q), (k_weight, span_k)):
+            if w is not None:
+                if w.dtype not in (torch.float32, torch.bfloat16) or w.numel() != span or not w.is_contiguous():
+                    raise KernelError("norm_turn_store: a norm's weight is as long as what is normed together, float32 or bfloat16")
+                w_f32 = 1 if w.dtype == torch.float32 else 0
+        if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+            raise KernelError("norm_turn_store: the two weights must be of one dtype")
+        if row_pos.dtype != torch.int32 or row_seq.dtype != torch.int32 or row_pos.numel() < n or row_seq.numel() < n:
+            raise KernelError("norm_turn_store: int32 sequences and positions, one per row")
+        h = lib("attention_scored")
+        _check(h.kvad_norm_turn_store(self.code, _ptr(q), ld_q, _ptr(k_src), ld_k, _ptr(v_src), ld_v, _ptr(q_weight), _ptr(k_weight), w_f32,
+                                      int(span_q), int(span_k), int(span_q), int(span_k), float(eps), _ptr(inv_freq if dims else None), int(dims),
+                                      float(mscale), _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(k_pages),
+                                      _ptr(v_pages), n, int(n_heads), n_kv, n_v, dk, dv, page, _stream()), h)
+
+    def diff_combine(self, maps, out, n_heads: int, group: int, lam: float, eps: float, gain: float) -> None:
+        """out[r, h] = gain * o / sqrt(mean(o^2) + eps), o = a1 - lam * a2 over a head's values, where `maps` (float32
+        [rows, 2 heads x dv]) holds the two maps' outputs as [kv head][map][head of the group][dv] and h = kv head x group + head
+        of the group."""
+        _need_cuda(maps, out)
+        n, total = out.shape
+        dv = total // n_heads
+        if (maps.dtype != torch.float32 or out.dtype != self.dtype or maps.shape != (n, 2 * total) or dv * n_heads != total or n_heads % group):
+            raise KernelError(f"diff_combine: float32 maps [rows, 2 heads x dv] and an output [rows, heads x dv] of {self.dtype}")
+        h = lib("attention_scored")
+        _check(h.kvad_diff_combine(self.code, _ptr(maps), _rows_view(maps, "maps"), _ptr(out), _rows_view(out, "diff_combine output"), n, int(n_heads),
+                                   int(group), dv, float(lam), float(eps), float(gain), _stream()), h)
+
     def latent_store(self, src, weight, eps: float, inv_freq, row_seq, row_pos, page_table, pages, rank: int, rot: int, *,
                      interleaved: bool) -> None:
         """Rows `[rows, rank + rot]`: the first `rank` entries RMS-normalised with `weight`, the last `rot` turned by the
@@ -884,14 +974,16 @@ class Ops:
     def attention_scored(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages, n_heads: int,
                          scale: float, *, value_dim: Optional[int] = None, softcap: float = 0.0, slope_span: float = 0.0,
                          window: int = 0, keep_first: int = 0, gate=None, heads_per_block: int = 1, n_splits: int = 1,
-                         scratch=None) -> None:
+                         scratch=None, key_maps: int = 1) -> None:
         """Softmax attention of packed rows (each sequence's rows are its last positions) over the paged cache with
         shaped scores: s = q.k * scale, capped by `softcap` * tanh(s / softcap) if positive, less slope_h * distance with
         slope_h = 2^(-slope_span (h+1) / n_heads) if `slope_span` is positive; a row sees the last `window` positions
         (0: all) and always the first `keep_first`.  `v_pages` None: the values are the first `value_dim` entries of the
         keys.  `gate`: the output is multiplied by sigmoid(gate).  `n_splits` > 1 (single-token rows): the keys of a
         row and head are dealt out to that many blocks and merged by a second kernel through `scratch` (float32, rows x
-        heads x n_splits x (value size + 2)).  32-bit arithmetic on the CUDA cores."""
+        heads x n_splits x (value size + 2)).  `key_maps` > 1: that many consecutive key heads read one value head (the values'
+        pages have kv heads / key_maps heads).  `out` may be float32 whatever the compute dtype (no gate then).  32-bit
+        arithmetic on the CUDA cores."""
         _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages, gate)
         ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
         _, n_kv, page, dk = k_pages.shape
@@ -899,12 +991,16 @@ class Ops:
             dv, v_ptr = int(value_dim or dk), k_pages
         else:
             dv, v_ptr = v_pages.shape[3], v_pages
-            if v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != self.dtype or not v_pages.is_contiguous():
+            if (v_pages.shape[0] != k_pages.shape[0] or v_pages.shape[1] * key_maps != n_kv or v_pages.shape[2] != page
+                    or v_pages.dtype != self.dtype or not v_pages.is_contiguous()):
                 raise KernelError("attention_scored: the values' pages must match the keys'")
         if q.shape[1] != n_heads * dk or out.shape != (q.shape[0], n_heads * dv):
             raise KernelError("attention_scored: queries/output do not match heads x sizes")
-        if {q.dtype, out.dtype, k_pages.dtype} != {self.dtype} or not k_pages.is_contiguous():
+        if {q.dtype, k_pages.dtype} != {self.dtype} or out.dtype not in (self.dtype, torch.float32) or not k_pages.is_contiguous():
             raise KernelError(f"attention_scored: tensors must be {self.dtype}")
+        out_f32 = out.dtype == torch.float32 and self.dtype != torch.float32
+        if out_f32 and gate is not None:
+            raise KernelError("attention_scored: a float32 output takes no gate")
         ld_g = 0
         if gate is not None:
             ld_g = _rows_view(gate, "attention gate")
@@ -918,7 +1014,7 @@ class Ops:
                                        _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_ptr), int(n_seqs), int(n_heads), n_kv,
                                        dk, dv, page, int(max_new), int(heads_per_block), float(scale), float(softcap or 0.0),
                                        float(slope_span or 0.0), int(window or 0), int(keep_first or 0), int(n_splits),
-                                       _ptr(scratch if n_splits > 1 else None), _stream()), h)
+                                       _ptr(scratch if n_splits > 1 else None), int(key_maps), int(out_f32), _stream()), h)
         if n_splits > 1:
             global _launches
             _launches += 1          # the merge kernel
@@ -935,18 +1031,25 @@ class Ops:
     # -- retention ------------------------------------------------------------------------
     def retention(self, q, k, v, out, state, seq_starts, kv_lens, seq_slots, n_seqs: int, decay, n_heads: int, *, inv_freq=None,
                   rot_dims: int = 0, interleaved: bool = False, k_scale: float = 1.0, gate=None, unit_norm_eps: Optional[float] = None,
-                  raw=None) -> None:
+                  raw=None, silu_inputs: bool = False, raw_only: bool = False) -> None:
         """Per sequence and head, over the step's rows in order: S = decay_h S + k v^T, o = S^T q, with q and k turned by
         position first (`inv_freq`, `rot_dims`), k scaled by `k_scale`; `unit_norm_eps`: o over its root mean square per
         head; `gate`: times silu(gate).  `state` is `[slots, heads, dk, dv]` float32 and is carried on.  `raw`: float32
-        scratch `[rows, heads x dv]`, needed where `retention_needs_raw` says so (a head's columns spread over blocks)."""
+        scratch `[rows, heads x dv]`, needed where `retention_needs_raw` says so (a head's columns spread over blocks).
+        `silu_inputs`: q, k and v pass a silu first (32-bit).  `raw_only`: the 32-bit read-outs in `raw` are all that is
+        written (`out` may be None; no norm, no gate)."""
         _need_cuda(q, k, v, out, state, seq_starts, kv_lens, seq_slots, decay, inv_freq, gate)
-        ld_q, ld_k, ld_v, ld_o = (_rows_view(t, "retention rows") for t in (q, k, v, out))
+        if raw_only:
+            if raw is None or gate is not None or unit_norm_eps is not None:
+                raise KernelError("retention: raw read-outs go to `raw`, without norm or gate")
+            out = q.new_empty((q.shape[0], 0)) if out is None else out
+        ld_q, ld_k, ld_v = (_rows_view(t, "retention rows") for t in (q, k, v))
+        ld_o = 0 if raw_only else _rows_view(out, "retention rows")
         if state.dim() != 4 or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1] != n_heads:
             raise KernelError("retention: the state must be contiguous float32 [slots, heads, dk, dv]")
         dk, dv = state.shape[2], state.shape[3]
         n = q.shape[0]
-        if (q.shape[1] != n_heads * dk or k.shape != q.shape or v.shape != (n, n_heads * dv) or out.shape != v.shape
+        if (q.shape[1] != n_heads * dk or k.shape != q.shape or v.shape != (n, n_heads * dv) or (not raw_only and out.shape != v.shape)
                 or {q.dtype, k.dtype, v.dtype, out.dtype} != {self.dtype}):
             raise KernelError(f"retention: rows must be {self.dtype} and match heads x sizes of the state")
         if decay.dtype != torch.float32 or decay.numel() != n_heads:
@@ -964,7 +1067,29 @@ class Ops:
         _check(h.kvad_retention(self.code, _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gate), ld_g, _ptr(out), ld_o, _ptr(raw), n, _ptr(state),
                                 _ptr(seq_starts), _ptr(kv_lens), _ptr(seq_slots), _ptr(decay), _ptr(inv_freq), int(rot_dims),
                                 int(bool(interleaved)), int(n_seqs), int(n_heads), dk, dv, float(k_scale),
-                                float(unit_norm_eps or 0.0), 0 if unit_norm_eps is None else 1, _stream()), h)
+                                float(unit_norm_eps or 0.0), 0 if unit_norm_eps is None else 1, int(bool(silu_inputs)), 0 if raw_only else 1,
+                                _stream()), h)
+
+    def row_norm_gate(self, raw, gate, weight, out, eps: float) -> None:
+        """out = raw / sqrt(mean over the row (raw^2) + eps) * weight * sigmoid(gate): `raw` float32, `gate` (may be None) and
+        `out` of the compute dtype, `weight` one per column (may be None)."""
+        _need_cuda(raw, gate, weight, out)
+        n, width = raw.shape
+        if raw.dtype != torch.float32 or out.dtype != self.dtype or out.shape != raw.shape:
+            raise KernelError(f"row_norm_gate: float32 input and {self.dtype} output of one shape")
+        ld_g = 0
+        if gate is not None:
+            ld_g = _rows_view(gate, "gate")
+            if gate.shape != raw.shape or gate.dtype != self.dtype:
+                raise KernelError("row_norm_gate: the gate must have the output's shape and dtype")
+        w_f32 = 0
+        if weight is not None:
+            if weight.numel() != width or weight.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("row_norm_gate: the weight must have the row's width, float32 or bfloat16")
+            w_f32 = 1 if weight.dtype == torch.float32 else 0
+        h = lib("retention")
+        _check(h.kvad_row_norm_gate(self.code, _ptr(raw), _rows_view(raw, "read-outs"), _ptr(gate), ld_g, _ptr(weight), w_f32, _ptr(out),
+                                    _rows_view(out, "row_norm_gate output"), n, width, float(eps), _stream()), h)
 
     def retention_needs_raw(self, dk: int, dv: int) -> bool:
         return lib("retention").kvad_retention_needs_raw(int(dk), int(dv)) == 1
@@ -1103,7 +1228,7 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_moe_route(_ptr(logits), _rows_view(logits, "router logits"), n, E, int(top), _ptr(chosen), _ptr(weight), _stream()), h)
 
-    ROUTINGS = {"top_logits": 0, "scores": 1}
+    ROUTINGS = {"top_logits": 0, "scores": 1, "sigmoid": 2}
 
     def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos, *, logits=None, weight=None,
                  routing: str = "top_logits", correction=None, n_real: Optional[int] = None) -> None:
@@ -1112,7 +1237,8 @@ class Ops:
         `slot_pos` [rows x top]: where each slot went.  With `logits` and `weight` the same launch routes the rows first
         (as `moe_route` does) and writes `chosen` and `weight`.  `routing` "scores": the scores are the softmax over all
         experts, the `top` largest of score + `correction` (float32, one per expert, or None) are chosen and weigh their
-        scores over the chosen scores' sum.  `n_real` < `n_experts`: the experts from `n_real` on have no matrices; their
+        scores over the chosen scores' sum.  `routing` "sigmoid": the `top` largest logits are chosen and each weighs in with the
+        sigmoid of its own logit, not renormalised.  `n_real` < `n_experts`: the experts from `n_real` on have no matrices; their
         slots get no position (`slot_pos` -1)."""
         _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos, logits, weight, correction)
         if correction is not None and (correction.dtype != torch.float32 or correction.numel() != n_experts):
@@ -1185,9 +1311,25 @@ class Ops:
         _check(h.kvad_clamped_glu(self.code, _ptr(gate), ld_g, _ptr(up), ld_u, _ptr(out), ld_o, gate.shape[0], gate.shape[1], float(limit),
                                   float(alpha), _stream()), h)
 
-    def moe_combine(self, residual, outs, slot_pos, weight, identity_input=None) -> None:
+    def scaled_glu(self, gate, up, out, act: str = "silu", slot=None, scale=None) -> None:
+        """out = act(s g) * (s u) with s = scale[slot[p]] for row p (`slot` int32 per row, -1: padding, whose output is zero;
+        `scale` float32 per (row, choice) pair; both None: s = 1): a gated expert whose INPUT is scaled by the router's weight,
+        W (s h) = s (W h).  act: silu or gelu_tanh; 32-bit arithmetic."""
+        _need_cuda(gate, up, out, slot, scale)
+        ld_g, ld_u, ld_o = _rows_view(gate, "gate"), _rows_view(up, "up"), _rows_view(out, "scaled_glu output")
+        if gate.shape != up.shape or out.shape != gate.shape or {gate.dtype, up.dtype, out.dtype} != {self.dtype}:
+            raise KernelError(f"scaled_glu: needs three {self.dtype} tensors of one shape")
+        if (slot is None) != (scale is None) or (slot is not None and (slot.dtype != torch.int32 or slot.numel() < gate.shape[0]
+                                                                        or scale.dtype != torch.float32 or not scale.is_contiguous())):
+            raise KernelError("scaled_glu: an int32 pair per row and a float32 scale per pair, or neither")
+        h = lib("moe")
+        _check(h.kvad_scaled_glu(self.code, _ptr(gate), ld_g, _ptr(up), ld_u, _ptr(out), ld_o, _ptr(slot), _ptr(scale), gate.shape[0], gate.shape[1],
+                                 self.GATES[act], _stream()), h)
+
+    def moe_combine(self, residual, outs, slot_pos, weight, identity_input=None, top: Optional[int] = None) -> None:
         """residual[r] += sum_k weight[r, k] * outs[slot_pos[r * top + k]], the choices in order (all float32); a slot
-        without a position (-1: an expert whose output is its input) adds weight[r, k] * identity_input[r]."""
+        without a position (-1: an expert whose output is its input) adds weight[r, k] * identity_input[r].  `weight` None
+        (then `top` says how many choices a row has): every weight is 1."""
         _need_cuda(residual, outs, slot_pos, weight, identity_input)
         ld_in, in_code = 0, F32
         if identity_input is not None:
@@ -1195,9 +1337,9 @@ class Ops:
             if identity_input.shape != residual.shape:
                 raise KernelError("moe_combine: the experts' input must have the stream's shape")
         n, width = residual.shape
-        top = weight.shape[1]
-        if (any(t.dtype != torch.float32 for t in (residual, outs, weight)) or not residual.is_contiguous() or not weight.is_contiguous()
-                or weight.shape[0] != n or outs.shape[1] != width or slot_pos.dtype != torch.int32 or slot_pos.numel() < n * top):
+        top = weight.shape[1] if weight is not None else int(top)
+        if (any(t.dtype != torch.float32 for t in (residual, outs) + (() if weight is None else (weight,))) or not residual.is_contiguous()
+                or (weight is not None and (not weight.is_contiguous() or weight.shape[0] != n)) or outs.shape[1] != width or slot_pos.dtype != torch.int32 or slot_pos.numel() < n * top):
             raise KernelError("moe_combine: float32 stream [rows, width], expert outputs [positions, width], weights [rows, top], int32 places")
         h = lib("moe")
         _check(h.kvad_moe_combine(_ptr(residual), _ptr(outs), _rows_view(outs, "expert outputs"), _ptr(slot_pos), _ptr(weight), n, width, top,

@@ -2,7 +2,7 @@
 from .base import (FAMILIES, Block, FeedForward, Mixer, Norm, Part, PartSpec, PositionEncoding,
                    build_part, part_kinds, register_part, unregister_part)
 from .linear import FusedLinear, Linear
-from . import norms, positions, attention, retention, latent_attention, matrix_memory, delta_rule, min_gru, feedforward, routed_mlp, block, ends  # noqa: F401  (register the built-in kinds)
+from . import norms, positions, attention, retention, side_by_side, latent_attention, matrix_memory, delta_rule, min_gru, feedforward, routed_mlp, block, ends  # noqa: F401  (register the built-in kinds)
 from .norms import LayerNorm
 from .positions import LearnedAbsolute, NoPositions
 from .attention import CausalSelfAttention

@@ -126,7 +126,9 @@ class ShapedScoreAttention(Mixer):
     keys are kept.  `value_position`: a rotary encoding over the whole value - the value of position j is turned
     by j before it is kept, and each head's weighted sum at position i is turned back by i (before the gate), so
     that what a query reads of a value depends on their distance.  `bias_suffix`: q, k, v and the output
-    projection have biases (`<name><suffix>`).  The projections are tensors of their own (`[out, in]`) and run as
+    projection have biases (`<name><suffix>`).  `qk_norm` {span: "head" | "all", eps, q_name, k_name}: queries and
+    keys are RMS-normed before they are turned, head by head with one weight as long as a head, or over the whole
+    projection with a weight as long as it.  The projections are tensors of their own (`[out, in]`) and run as
     one product."""
     graph_safe = True
     kernel_families = ("scored_attention", "norm_rotary")
@@ -137,13 +139,20 @@ class ShapedScoreAttention(Mixer):
                  value_blend: Optional[str] = None, gate: bool = False, q_name: str = "q", k_name: str = "k",
                  v_name: str = "v", gate_name: str = "g", out_name: str = "o", blend_name: str = "vmix",
                  blend_key: str = "first_values", position: Optional[PartSpec] = None, value_position: Optional[PartSpec] = None,
-                 bias_suffix: Optional[str] = None):
+                 bias_suffix: Optional[str] = None, qk_norm: Optional[dict] = None):
         super().__init__(prefix)
         self.width, self.n_heads, self.key_dim = int(width), int(n_heads), int(key_dim)
         self.n_kv_heads = int(n_kv_heads) if n_kv_heads else self.n_heads
         self.value_dim = int(value_dim) if value_dim else self.key_dim
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv_heads} key/value heads")
+        self.qk_norm = dict(qk_norm) if qk_norm else None
+        if self.qk_norm is not None:
+            if self.qk_norm.get("span") not in ("head", "all"):
+                raise ValueError("attention: queries and keys are normed by `head` or `all` together")
+            if value_blend or value_position is not None:
+                raise ValueError("attention: normed queries and keys go with plain values")
+        self.q_norm = self.k_norm = None
         if value_blend not in (None, "source", "blend"):
             raise ValueError("value_blend is None, `source` or `blend`")
         self.score_scale = float(score_scale)
@@ -166,6 +175,10 @@ class ShapedScoreAttention(Mixer):
         self.value_position = build_part("position", value_position, prefix) if value_position is not None else None
         if self.position is not None and self.position.dims > self.key_dim:
             raise ValueError("attention: the rotary encoding turns more entries than a key has")
+        if self.qk_norm is not None and self.position is not None and self.position.interleaved:
+            raise ValueError("attention: normed queries and keys are turned in pairs half apart")
+        if self.qk_norm is None and self.position is not None and self.position.mscale != 1.0:
+            raise ValueError("attention: stretched frequencies are applied together with the queries' and keys' norm")
         if self.value_position is not None and self.value_position.dims != self.value_dim:
             raise ValueError("attention: the values' rotary encoding turns the whole value")
         if self.value_position is not None and self.value_blend:
@@ -183,15 +196,27 @@ class ShapedScoreAttention(Mixer):
     def children(self):
         return [self.proj, self.out] + [p for p in (self.position, self.value_position) if p is not None]
 
+    def _norm_spans(self):
+        whole = self.qk_norm["span"] == "all"
+        return (self.q_width if whole else self.key_dim), (self.k_width if whole else self.key_dim)
+
     def own_requests(self):
-        return [TensorRequest(self.prefix + self.blend_name, ())] if self.value_blend else []
+        out = [TensorRequest(self.prefix + self.blend_name, ())] if self.value_blend else []
+        if self.qk_norm is not None:
+            sq, sk = self._norm_spans()
+            out += [TensorRequest(self.prefix + self.qk_norm.get("q_name", "q.norm"), (sq,)),
+                    TensorRequest(self.prefix + self.qk_norm.get("k_name", "k.norm"), (sk,))]
+        return out
 
     def load_own(self, fetch):
         if self.value_blend:
             self.blend = fetch(self.prefix + self.blend_name, keep_f32=True).reshape(1)
+        if self.qk_norm is not None:
+            self.q_norm = fetch(self.prefix + self.qk_norm.get("q_name", "q.norm"), keep_f32=True).float().contiguous()
+            self.k_norm = fetch(self.prefix + self.qk_norm.get("k_name", "k.norm"), keep_f32=True).float().contiguous()
 
     def own_tensors(self):
-        return [self.blend] if self.blend is not None else []
+        return [t for t in (self.blend, self.q_norm, self.k_norm) if t is not None]
 
     def cache_need(self):
         return KVNeed(self.n_kv_heads, self.key_dim, self.window, value_dim=self.value_dim, keep_first=self.keep_first)
@@ -205,7 +230,17 @@ class ShapedScoreAttention(Mixer):
         view = ctx.kv(call.cache)
         other = None
         turns = self.position is not None or self.value_position is not None
-        if turns and call.writes_cache and not self.value_blend:      # one launch turns queries, keys and values and stores the latter two
+        if self.qk_norm is not None:        # norm, turn and store in one launch
+            if not call.writes_cache:
+                raise ValueError("attention: normed queries and keys come with a cache entry of the layer's own")
+            pos = self.position
+            sq, sk = self._norm_spans()
+            ops.norm_turn_store(q, k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages, self.n_heads,
+                                q_weight=self.q_norm, k_weight=self.k_norm, span_q=sq, span_k=sk, eps=float(self.qk_norm["eps"]),
+                                inv_freq=pos.inv_freq if pos is not None else None, dims=pos.dims if pos is not None else 0,
+                                mscale=pos.mscale if pos is not None else 1.0)
+            stored = True
+        elif turns and call.writes_cache and not self.value_blend:      # one launch turns queries, keys and values and stores the latter two
             pos, vpos = self.position, self.value_position
             ops.turn_store(q, k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages, self.n_heads,
                            inv_freq=pos.inv_freq if pos is not None else None, dims=pos.dims if pos is not None else 0,
@@ -251,5 +286,107 @@ class ShapedScoreAttention(Mixer):
         self.out.forward(ctx, mixed, residual, "residual")
 
 
+class DifferentialAttention(Mixer):
+    """Two softmax attentions ("maps") per head over the same values, the second taken off the first:
+
+        q = W_q h + b: heads x 2 x key_dim, k = W_k h + b: kv heads x 2 x key_dim (head by head as [map 1, map 2]),
+        v = W_v h + b: kv heads x value_dim;  every (head, map) of q and k RMS-normed over key_dim with one shared weight
+        each (`qk_norm`), then turned by position (`position`, pairs half apart, possibly stretched frequencies);
+        a_m = softmax(q_m . k_m * score_scale over the window) v                       (m = 1, 2)
+        o = a_1 - lam a_2,  lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff                (one number a layer)
+        o <- (1 - diff) o / sqrt(mean(o^2) + eps) per head, then the output projection.
+
+    The maps are key heads of their own in the cache - [kv head][map] - that share the kv head's values
+    (`KVNeed.value_heads`), so one launch of the scored attention runs both over one copy of the values; the queries'
+    rows are ordered [kv head][map][head of the group] when they are loaded, which makes every map's heads a group
+    of that launch.  Scores, softmax weights, both maps' outputs, their difference and the unit norm are 32-bit."""
+    graph_safe = True
+    kernel_families = ("scored_attention", "norm_rotary")
+
+    def __init__(self, prefix: str, width: int, n_heads: int, key_dim: int, value_dim: int, score_scale: float, diff: float, eps: float,
+                 n_kv_heads: Optional[int] = None, window: Optional[int] = None, position: Optional[PartSpec] = None, qk_norm: bool = True,
+                 bias_suffix: Optional[str] = ".b", q_name: str = "q", k_name: str = "k", v_name: str = "v", out_name: str = "o",
+                 q_norm_name: str = "q.norm", k_norm_name: str = "k.norm", lambda_names=("lq1", "lk1", "lq2", "lk2")):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.key_dim, self.value_dim = int(width), int(n_heads), int(key_dim), int(value_dim)
+        self.n_kv_heads = int(n_kv_heads) if n_kv_heads else self.n_heads
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv_heads} key/value heads")
+        self.group = self.n_heads // self.n_kv_heads
+        self.score_scale, self.diff, self.eps = float(score_scale), float(diff), float(eps)
+        self.window = int(window) if window else None
+        self.q_width, self.k_width = 2 * self.n_heads * self.key_dim, 2 * self.n_kv_heads * self.key_dim
+        self.v_width, self.o_width = self.n_kv_heads * self.value_dim, self.n_heads * self.value_dim
+        self.q_name = q_name
+        self.proj = FusedLinear(prefix, self.width, [(q_name, self.q_width), (k_name, self.k_width), (v_name, self.v_width)],
+                                bias_suffix=bias_suffix)
+        self.out = Linear(prefix + out_name, self.o_width, self.width, bias=False, weight_name="")
+        self.position = build_part("position", position, prefix) if position is not None else None
+        if self.position is not None and (self.position.dims > self.key_dim or self.position.interleaved):
+            raise ValueError("differential attention: pairs half apart, at most a key's entries")
+        self.normed, self.norm_names, self.lambda_names = bool(qk_norm), (q_norm_name, k_norm_name), tuple(lambda_names)
+        self.q_norm = self.k_norm = None
+        self.lam = None
+        self.heads_per_block = max(d for d in (1, 2, 4) if self.group % d == 0)
+
+    def children(self):
+        return [self.proj, self.out] + ([self.position] if self.position is not None else [])
+
+    def own_requests(self):
+        out = [TensorRequest(self.prefix + n, (self.key_dim,)) for n in self.lambda_names]
+        if self.normed:
+            out += [TensorRequest(self.prefix + n, (self.key_dim,)) for n in self.norm_names]
+        return out
+
+    def load(self, fetch):
+        super().load(fetch)
+        # the queries' rows from [head][map] to [kv head][map][head of the group]
+        G, g, dk = self.n_kv_heads, self.group, self.key_dim
+        order = torch.arange(self.q_width, device=self.proj.weight.device).view(G, g, 2, dk).permute(0, 2, 1, 3).reshape(-1)
+        cols = self.proj.columns(0)
+        self.proj.weight[cols] = self.proj.weight[cols][order]
+        if self.proj.bias is not None:
+            self.proj.bias[cols] = self.proj.bias[cols][order]
+
+    def load_own(self, fetch):
+        lq1, lk1, lq2, lk2 = (fetch(self.prefix + n, keep_f32=True).double().cpu() for n in self.lambda_names)
+        self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum())) + self.diff
+        if self.normed:
+            self.q_norm, self.k_norm = (fetch(self.prefix + n, keep_f32=True).float().contiguous() for n in self.norm_names)
+
+    def own_tensors(self):
+        return [t for t in (self.q_norm, self.k_norm) if t is not None]
+
+    def cache_need(self):
+        return KVNeed(2 * self.n_kv_heads, self.key_dim, self.window, value_dim=self.value_dim, value_heads=self.n_kv_heads)
+
+    def forward(self, ctx, h, residual, call):
+        if not call.writes_cache:
+            raise ValueError("differential attention: every call has a cache entry of its own")
+        n, ops, b = h.shape[0], ctx.ops, ctx.batch
+        buf = ctx.buffer((n, self.proj.out_features))
+        self.proj.forward(ctx, h, buf)
+        q, k, v = (buf[:, self.proj.columns(i)] for i in range(3))
+        view, pos = ctx.kv(call.cache), self.position
+        ops.norm_turn_store(q, k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages, 2 * self.n_heads,
+                            q_weight=self.q_norm, k_weight=self.k_norm, span_q=self.key_dim if self.normed else 0,
+                            span_k=self.key_dim if self.normed else 0, eps=self.eps, inv_freq=pos.inv_freq if pos is not None else None,
+                            dims=pos.dims if pos is not None else 0, mscale=pos.mscale if pos is not None else 1.0)
+        maps = ctx.buffer((n, 2 * self.o_width), torch.float32)
+        splits, scratch = 1, None
+        if b.is_decode:
+            reach = self.window if self.window else view.page_table.shape[1] * view.page_size
+            splits = ops.scored_splits(n, 2 * self.n_kv_heads, self.group, reach)
+            scratch = ctx.buffer((n * 2 * self.n_heads * splits * (self.value_dim + 2),), torch.float32) if splits > 1 else None
+        ops.attention_scored(q, maps, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages, view.v_pages,
+                             2 * self.n_heads, self.score_scale, window=self.window or 0,
+                             heads_per_block=min(self.group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch,
+                             key_maps=2)
+        mixed = ctx.buffer((n, self.o_width))
+        ops.diff_combine(maps, mixed, self.n_heads, self.group, self.lam, self.eps, 1.0 - self.diff)
+        self.out.forward(ctx, mixed, residual, "residual")
+
+
+register_part("mixer", "differential_attention", DifferentialAttention)
 register_part("mixer", "causal_attention", CausalSelfAttention)
 register_part("mixer", "shaped_score_attention", ShapedScoreAttention)

@@ -3,7 +3,8 @@ read its output, their sum is scaled into the stream (the feed-forward may be ab
 (crates/llm/src/model/gpt2.rs:6-9, 229-266).  `sandwich`: a norm before AND after each sublayer,
 x += scale1 * norm1b(mixer(conv(norm1(x)))); x += scale2 * norm2b(ff(norm2(x))), with a gain per channel
 (`scale*`, may be absent), an optional short causal convolution that is added to the mixer's input
-(`input_conv`), and an optional feed-forward.  `stream_mix`: no sublayers - the stream is mixed with the
+(`input_conv`), and an optional feed-forward; with `pre_norm` a `stream_copy` the sublayers read the stream itself and
+only their results are normed, x += norm1(mixer(x)); x += norm2(ff(x)).  `stream_mix`: no sublayers - the stream is mixed with the
 embedding output, x <- W [x; x0] + v[turn], which is how a repeated range of layers starts each of its
 passes.  The residual stream stays in 32-bit; the parts add into it.
 """
@@ -135,15 +136,17 @@ class SandwichBlock(Block):
     kernel_families = ("norm_rotary",)
 
     def __init__(self, prefix: str, norm: PartSpec, mixer: PartSpec, feed_forward=None, input_conv: Optional[dict] = None,
-                 scaled: bool = True, norm1_name: str = "norm1", norm1b_name: str = "norm1b", norm2_name: str = "norm2",
+                 scaled: bool = True, pre_norm: Optional[PartSpec] = None, norm1_name: str = "norm1", norm1b_name: str = "norm1b", norm2_name: str = "norm2",
                  norm2b_name: str = "norm2b", scale1_name: str = "ls1", scale2_name: str = "ls2", mixer_name: str = "mix.",
                  feed_forward_name: str = "mlp."):
         super().__init__(prefix)
-        self.norm1 = build_part("norm", norm, prefix + norm1_name)
+        # `pre_norm`: what the sublayers read the stream through, if not `norm` (the norm of the results keeps `norm`'s width and eps)
+        before = pre_norm if pre_norm is not None else norm
+        self.norm1 = build_part("norm", before, prefix + norm1_name)
         self.mixer = build_part("mixer", mixer, prefix + mixer_name)
         self.conv = InputConvolution(prefix, **input_conv) if input_conv else None
         self.feed_forward = build_part("feed_forward", feed_forward, prefix + feed_forward_name) if feed_forward is not None else None
-        self.norm2 = build_part("norm", norm, prefix + norm2_name) if self.feed_forward is not None else None
+        self.norm2 = build_part("norm", before, prefix + norm2_name) if self.feed_forward is not None else None
         self.width, self.eps = int(norm.params["width"]), float(norm.params["eps"])
         self.scaled = bool(scaled)
         self.names = [(norm1b_name, scale1_name)] + ([(norm2b_name, scale2_name)] if self.feed_forward is not None else [])
@@ -157,6 +160,8 @@ class SandwichBlock(Block):
 
     def own_requests(self):
         out = []
+        if self.conv is not None and getattr(self.mixer, "extra_cache_need", None) is not None and self.mixer.extra_cache_need() is not None:
+            raise ValueError("sandwich: the input convolution and the mixer both want the call's `aux` cache entry")
         for norm_name, scale_name in self.names:
             out.append(TensorRequest(self.prefix + norm_name, (self.width,)))
             if self.scaled:

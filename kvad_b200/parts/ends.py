@@ -72,9 +72,12 @@ class LMHead(Part):
 
     def __init__(self, prefix: str, vocab_size: int, width: int, norm: PartSpec, tied: bool,
                  norm_name: str = "ln_f.", name: str = "lm_head.", bias: bool = False,
-                 embedding: Optional[TokenEmbedding] = None, weight_name: str = "weight"):
+                 embedding: Optional[TokenEmbedding] = None, weight_name: str = "weight", softcap: Optional[float] = None):
         super().__init__(prefix)
         self.vocab_size, self.width, self.tied = int(vocab_size), int(width), bool(tied)
+        self.softcap = float(softcap) if softcap else 0.0        # logits <- cap * tanh(logits / cap)
+        if self.softcap:
+            self.kernel_families = ("norm_rotary",)
         self.norm = build_part("norm", norm, prefix + norm_name)
         self.embedding = embedding
         if self.tied and embedding is None:
@@ -99,6 +102,8 @@ class LMHead(Part):
         if self.tied:
             self.proj.weight = self.embedding.weight
         self.proj.forward(ctx, h, logits, "store_f32")
+        if self.softcap:
+            ctx.ops.tanh_cap(logits, self.softcap)
         return logits
 
 

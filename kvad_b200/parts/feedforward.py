@@ -43,8 +43,8 @@ class GatedMLP(FeedForward):
     def __init__(self, prefix: str, width: int, hidden: int, activation: str = "silu", gate_name: str = "gate",
                  up_name: str = "up", down_name: str = "down"):
         super().__init__(prefix)
-        if activation not in ("silu", "sigmoid", "relu"):
-            raise ValueError(f"gated_mlp has no activation `{activation}`; it has silu, sigmoid and relu")
+        if activation not in ("silu", "sigmoid", "relu", "gelu_tanh"):
+            raise ValueError(f"gated_mlp has no activation `{activation}`; it has silu, sigmoid, relu and gelu_tanh")
         self.width, self.hidden, self.activation = int(width), int(hidden), activation
         self.gate_up = FusedLinear(prefix, self.width, [(gate_name, self.hidden), (up_name, self.hidden)])
         self.down = Linear(prefix + down_name, self.hidden, self.width, bias=False, weight_name="")

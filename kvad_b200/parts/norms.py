@@ -101,5 +101,47 @@ class RMSNorm(Norm):
         return out
 
 
+class StreamCopy(Norm):
+    """No norm at all: the rows of the stream as they are, in the compute dtype - for sublayers that read the stream
+    itself and whose RESULTS are normed (`PostNorm`).  Like `rmsnorm` it takes up a sum that a block before it still
+    owes to the stream, in the same pass over the rows.  In the 32-bit engine the stream itself is handed on."""
+    graph_safe = True
+    kernel_families = ("norm_rotary",)
+    takes_deferred = True
+
+    def __init__(self, prefix: str, width: int):
+        super().__init__(prefix)
+        self.width = int(width)
+
+    def forward(self, ctx, x, rows=None, n_rows=None, out=None):
+        n = n_rows if n_rows is not None else (x.shape[0] if rows is None else rows.numel())
+        deferred = ctx.shared.get("deferred_residual") if x.dtype == torch.float32 else None
+        if deferred is not None and deferred[0] is not x:
+            deferred = None
+        same = ctx.dtype == torch.float32 and rows is None and out is None       # (the reader can take the stream itself)
+        if deferred is not None and not isinstance(deferred[2], PostNorm):
+            if rows is not None:
+                raise ValueError("stream_copy: a scaled sum is taken up with all rows")
+            from .block import flush_deferred
+            flush_deferred(ctx)
+            deferred = None
+        if deferred is not None:
+            _, delta, post = deferred
+            if same:
+                ctx.ops.postnorm_rmsnorm(x[:ctx.n_rows], delta[:ctx.n_rows], post.gain, post.eps)
+            else:
+                out = ctx.buffer((n, self.width)) if out is None else out
+                ctx.ops.postnorm_rmsnorm(x[:ctx.n_rows], delta[:ctx.n_rows], post.gain, post.eps, out, rows=rows, plain_out=True)
+            if rows is None:
+                ctx.shared.pop("deferred_residual")
+            return x[:n] if same else out
+        if same:
+            return x[:n]
+        out = ctx.buffer((n, self.width)) if out is None else out
+        ctx.ops.cast_rows(x, out, rows)
+        return out
+
+
+register_part("norm", "stream_copy", StreamCopy)
 register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "rmsnorm", RMSNorm)

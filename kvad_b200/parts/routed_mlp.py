@@ -18,6 +18,12 @@ correction only steers the choice), and the chosen weigh in with their s over th
 last `identity` router outputs are experts without matrices whose output is their input.  An optional shared expert of
 the same form runs for every row, times sigmoid(w_sg . h), one number per row.  Same grouping, grouped products and
 ordered sum as `routed_mlp`.
+
+`input_scaled_routed_mlp`: gated experts out = W_down (act(W_gate x) * (W_up x)) (act = silu), no biases, chosen by the
+`top` largest sigmoid scores s = sigmoid(W_router h) (32-bit), which are not renormalised and scale the expert's INPUT:
+the output is the sum over the chosen of expert(s h).  Since the first two products are linear, s is applied to their
+results where the gate is computed.  An optional shared expert (`gated_mlp` with the same activation) runs for every
+row.  Same grouping, grouped products and ordered sum (with unit weights) as `routed_mlp`.
 """
 from __future__ import annotations
 
@@ -198,6 +204,80 @@ class ScoreRoutedMLP(FeedForward):
             self.shared_down.forward(ctx, hid, residual, "residual")
 
 
+class InputScaledRoutedMLP(FeedForward):
+    graph_safe = True
+    kernel_families = ("moe", "norm_rotary")
+
+    def __init__(self, prefix: str, width: int, n_experts: int, top: int, hidden: int, activation: str = "silu", shared: Optional[dict] = None,
+                 router_name: str = "router", expert_name: str = "e{}.", shared_name: str = "shared.", gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down"):
+        super().__init__(prefix)
+        self.width, self.n_experts, self.top, self.hidden = int(width), int(n_experts), int(top), int(hidden)
+        if not (1 <= self.top <= self.n_experts):
+            raise ValueError(f"input_scaled_routed_mlp: every row uses {top} of {n_experts} experts")
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError("input_scaled_routed_mlp: the experts' activation is silu or gelu_tanh")
+        self.activation = activation
+        self.router = Linear(prefix + router_name, self.width, self.n_experts, bias=False, weight_name="")
+        if shared:
+            from .feedforward import GatedMLP
+            self.shared = GatedMLP(prefix + shared_name, self.width, int(shared["hidden"]), activation=shared.get("activation", activation),
+                                   gate_name=gate_name, up_name=up_name, down_name=down_name)
+        else:
+            self.shared = None
+        self.names = dict(expert=expert_name, gate=gate_name, up=up_name, down=down_name)
+        self.w_in = None           # [experts, 2 hidden, width]: every expert's gate rows, then its up rows
+        self.w_out = None          # [experts, width, hidden]
+
+    def children(self):
+        return [self.router] + ([self.shared] if self.shared is not None else [])
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(e) + self.names[which]
+
+    def own_requests(self):
+        out = []
+        for e in range(self.n_experts):
+            out += [TensorRequest(self._expert(e, "gate"), (self.hidden, self.width)), TensorRequest(self._expert(e, "up"), (self.hidden, self.width)),
+                    TensorRequest(self._expert(e, "down"), (self.width, self.hidden))]
+        return out
+
+    def load_own(self, fetch):
+        self.w_in = torch.stack([torch.cat([fetch(self._expert(e, "gate")), fetch(self._expert(e, "up"))], dim=0)
+                                 for e in range(self.n_experts)]).contiguous()
+        self.w_out = torch.stack([fetch(self._expert(e, "down")) for e in range(self.n_experts)]).contiguous()
+
+    def own_tensors(self):
+        return [t for t in (self.w_in, self.w_out) if t is not None]
+
+    def forward(self, ctx, h, residual):
+        n, ops, E, top, ff = h.shape[0], ctx.ops, self.n_experts, self.top, self.hidden
+        logits = ctx.buffer((n, (E + 3) // 4 * 4), torch.float32)[:, :E]
+        self.router.forward(ctx, h, logits, "store_f32")
+        chosen, weight = ctx.buffer((n, top), torch.int32), ctx.buffer((n, top), torch.float32)
+        tm = ops.moe_tile_rows(n, top, self.width % 8 == 0 and ff % 8 == 0)
+        tiles = ops.moe_max_tiles(n, top, E, tm)
+        tile_expert, slot_pos = ctx.buffer((tiles,), torch.int32), ctx.buffer((n * top,), torch.int32)
+        pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
+        ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos, logits=logits, weight=weight, routing="sigmoid")
+        both = ctx.buffer((tiles * tm, 2 * ff))
+        few = n * top <= ops.MOE_FEW_SLOTS      # (by the step's shape only)
+        if tm == ops.MOE_WIDE_TILE:            # many rows: whole tiles on the tensor cores, from a copy of the rows in position order
+            rows = ctx.buffer((tiles * tm, self.width))
+            ops.gather_rows(h, pos_row, rows)
+            ops.grouped_linear(rows, self.w_in, both, tile_expert, pos_slot)
+        else:
+            ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row, few_rows=few)
+        hid = ctx.buffer((tiles * tm, ff))
+        ops.scaled_glu(both[:, :ff], both[:, ff:], hid, self.activation, slot=pos_slot, scale=weight)      # (the weight scales the input)
+        outs = ctx.buffer((tiles * tm, self.width), torch.float32)
+        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot, few_rows=few)
+        ops.moe_combine(residual, outs, slot_pos, None, top=top)
+        if self.shared is not None:
+            self.shared.forward(ctx, h, residual)
+
+
+register_part("feed_forward", "input_scaled_routed_mlp", InputScaledRoutedMLP)
 register_part("feed_forward", "clamped_glu_mlp", ClampedGluMLP)
 register_part("feed_forward", "score_routed_mlp", ScoreRoutedMLP)
 register_part("feed_forward", "routed_mlp", RoutedMLP)
