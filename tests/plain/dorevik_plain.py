@@ -131,7 +131,7 @@ def softmax_attention(q, k, v, scale, window):
 def differential_attention(h, w, p, m, eps):
     """Two maps per head over the same values; o = a1 - lam a2, unit norm per head, times (1 - diff)."""
     T = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, dk, dv = m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m["vdim"]
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H * 2, dk)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G * 2, dk)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
@@ -149,7 +149,7 @@ def differential_attention(h, w, p, m, eps):
 def windowed_attention(h, w, p, m, eps):
     """The left mixer: queries and keys normed over the whole projection, rotary, window, softmax."""
     T = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, dk, dv = m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m["vdim"]
     q = rms_norm(h @ w[p + "q"].T, w[p + "q.norm"], eps).reshape(T, H, dk)
     k = rms_norm(h @ w[p + "k"].T, w[p + "k.norm"], eps).reshape(T, G, dk)
     v = (h @ w[p + "v"].T).reshape(T, G, dv)
@@ -251,3 +251,10 @@ class Dorevik:
         if trace is not None:
             trace["streams"], trace["routed"] = streams, routed
         return z
+
+    def greedy(self, prompt, n):
+        """`n` tokens after `prompt`, each the largest logit's (the first of equals)."""
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(int(np.argmax(self.forward(toks)[-1])))
+        return toks[len(prompt):]
