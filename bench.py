@@ -285,25 +285,46 @@ def dopipel_config(width, ff, vocab, heads, dim):
             "loop": {"start": 1, "stop": 3, "times": 2}}
 
 
+def dorevik_config(width, ff, vocab, heads, dim, window):
+    """Layers that resemble a real model's: differential attention (grouped heads, keys of half a head so that a head's two maps
+    together are as long as the other designs' keys) and the two mixers side by side (windowed attention beside linear attention with
+    a decay, heads of 128 as in `nifulix_config`), dense and routed feed-forwards in turn (two chosen of eight experts plus a shared
+    expert: together as wide as the dense `ff`, as in `vepinex_config`)."""
+    rot = {"base": 1e4, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5, "diff": 0.3,
+                                          "mask": {"size": window}, "rot": rot}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads // 2, "kv_heads": heads // 8, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 1e6, "dims": dim // 2}},
+        "right": {"heads": width // 256, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - i % 6) for i in range(width // 256)]}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    layers = [dict(l, mlp=m) for l, m in ((att, dense), (att, moe), (par, dense), (att, moe), (att, dense), (par, moe))]
+    return {"architecture": "Dorevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers}
+
+
 def design_points(args, pk, pk_src):
     """`--design nifulix`: prefill and decode throughput of Nifulix at layer sizes that resemble a real model's, beside GPT-2 (the
     closest model this library runs) at the same width, depth, head size and weight count of the feed-forward; and, from
     a kernel-by-kernel pass with CUDA events around every operation, each design's mean time per operation.
     `--design vepinex`: the same for Vepinex beside Nifulix (recurrent, latent-attention and gated feed-forward layers of its own).
-    `--design dopipel`: the same for Dopipel beside Vepinex (routed feed-forwards, a recurrence and scored attention in both)."""
+    `--design dopipel`: the same for Dopipel beside Vepinex (routed feed-forwards, a recurrence and scored attention in both).
+    `--design dorevik`: the same for Dorevik beside Nifulix (windowed scored attention and linear attention with a decay in both)."""
     import torch
     from kvad_b200 import StepEntry, profile, write_random_model
 
     sizes = {"w1024": dict(width=1024, heads=16, dim=64, ff=2816, inner=4096), "w2048": dict(width=2048, heads=16, dim=128, ff=5632, inner=8192)}
     vocab, ctx, window, plen = 32000, 2048, 512, 512
-    first, second = {"nifulix": ("nifulix", "gpt2"), "vepinex": ("vepinex", "nifulix"), "dopipel": ("dopipel", "vepinex")}[args.design]
+    first, second = {"nifulix": ("nifulix", "gpt2"), "vepinex": ("vepinex", "nifulix"), "dopipel": ("dopipel", "vepinex"),
+                     "dorevik": ("dorevik", "nifulix")}[args.design]
     out = {"design": first, "beside": second, "dtype": args.dtype, "data": "synthetic: seeded uniform-random token ids, seeded random weights",
            "prefill": "one step of 2 x 1024 prompt tokens, L2 flushed between iterations", "decode": f"batch {args.batch}, {plen}-token prompts, {min(args.steps, 128)} steps after {max(3, args.warmup)} warm-up steps, tokens fed back on the device",
            "window": window, "sizes": {}}
     for name, z in sizes.items():
         row = {}
         for design in (first, second):
-            cfg = (dopipel_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "dopipel" else
+            cfg = (dorevik_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "dorevik" else
+                   dopipel_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "dopipel" else
                    vepinex_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "vepinex" else
                    nifulix_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "nifulix" else
                    dict(model_type="gpt2", n_layer=6, n_embd=z["width"], n_head=z["heads"], n_inner=z["inner"], vocab_size=vocab, n_positions=ctx,
@@ -412,9 +433,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="the same as --points none")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
                     help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix", "vepinex", "dopipel"],
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix", "vepinex", "dopipel", "dorevik"],
                     help="`nifulix`: instead of the headline, Nifulix beside GPT-2 at equal sizes (prefill, decode, time per operation); "
-                         "`vepinex`: Vepinex beside Nifulix; `dopipel`: Dopipel beside Vepinex")
+                         "`vepinex`: Vepinex beside Nifulix; `dopipel`: Dopipel beside Vepinex; `dorevik`: Dorevik beside Nifulix")
     args = ap.parse_args()
     if args.skip_points:
         args.points = "none"
@@ -440,7 +461,7 @@ def main():
     from kvad_b200 import write_random_model
 
     pk, pk_src = peaks()
-    if args.design in ("nifulix", "vepinex", "dopipel"):
+    if args.design in ("nifulix", "vepinex", "dopipel", "dorevik"):
         return design_points(args, pk, pk_src)
     tmp = tempfile.TemporaryDirectory(prefix="kvad_b200-bench-")
     model_dir = tmp.name

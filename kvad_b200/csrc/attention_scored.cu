@@ -48,6 +48,7 @@ struct ScoredArgs {
   int n_heads, n_kv_heads, dk, dv, hp, v_alias;
   int key_maps;          // this many consecutive key heads read one value head
   int out_f32;           // the output is 32-bit whatever the storage type (no gate then)
+  int merge;             // 0: with n_splits > 1 the parts are left in `partial` for a merge of the caller's
   float scale, softcap, slope_span;
   int window, keep_first;
   int vec_k, vec_v;      // keys / values can be fetched in 16-byte pieces
@@ -305,6 +306,55 @@ __global__ void scored_merge_kernel(const float* __restrict__ partial, int n_spl
   }
 }
 
+// The same merge for the two maps of a differential attention, and its last step with it: a block per (row, head of the
+// output) merges both maps' parts (`partial` rows are laid out [kv head][map][head of the group]), takes the second map
+// off the first with `lambda`, and writes o * gain / sqrt(mean(o^2) + eps).  A thread per value entry.
+template <typename T>
+__global__ void __launch_bounds__(128)
+scored_merge_diff_kernel(const float* __restrict__ partial, int n_splits, int n_heads, int group, int dv, T* __restrict__ out, int64_t ld_out,
+                         float lambda, float eps, float gain) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, h = blockIdx.y, kv = h / group, j = h - kv * group;
+  float o[4] = {0.f, 0.f, 0.f, 0.f};                    // (dv <= 512: four entries a thread at most)
+  float sq = 0.f;
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    const int hm = (kv * 2 + m) * group + j;
+    const float* src = partial + ((int64_t)row * 2 * n_heads + hm) * n_splits * (dv + 2);
+    float mx = -INFINITY;
+    for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, src[i * (dv + 2)]);
+    float total = 0.f;
+    for (int i = 0; i < n_splits; ++i) {
+      const float mi = src[i * (dv + 2)];
+      if (mi != -INFINITY) total = fmaf(src[i * (dv + 2) + 1], expf(mi - mx), total);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int d = threadIdx.x + 128 * t;
+      if (d < dv) {
+        float y = 0.f;
+        for (int i = 0; i < n_splits; ++i) {
+          const float mi = src[i * (dv + 2)];
+          if (mi != -INFINITY) y = fmaf(src[i * (dv + 2) + 2 + d], expf(mi - mx), y);
+        }
+        y /= total;
+        o[t] = m == 0 ? y : fmaf(-lambda, y, o[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) sq = fmaf(o[t], o[t], sq);
+  sq = block_sum(sq, scratch);
+  const float f = gain / sqrtf(sq / (float)dv + eps);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int d = threadIdx.x + 128 * t;
+    if (d < dv) out[(int64_t)row * ld_out + (int64_t)h * dv + d] = from_f32<T>(o[t] * f);
+  }
+}
+
 template <typename T, int KPL, int DPL, int NW>
 int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cudaStream_t stream) {
   constexpr int TR = RPW * NW, THREADS = 32 * NW;
@@ -318,7 +368,7 @@ int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cud
   dim3 grid(((max_new + tok - 1) / tok) * a.n_splits, n_seqs, a.n_kv_heads * chunks);
   kvad_launch(scored_attention_kernel<T, KPL, DPL, NW>, grid, dim3(THREADS), smem, stream, a);
   KVAD_CHECK_LAUNCH("attention_scored");
-  if (a.n_splits > 1) {       // (rows are single tokens here: row = sequence)
+  if (a.n_splits > 1 && a.merge) {       // (rows are single tokens here: row = sequence)
     kvad_launch(scored_merge_kernel<T>, dim3(n_seqs, a.n_heads), dim3(a.dv <= 64 ? 64 : 128), 0, stream, (const float*)a.partial, a.n_splits,
                 a.n_heads, a.dv, (T*)a.out, a.ld_out, (const T*)a.gate, a.ld_gate, a.out_f32);
     KVAD_CHECK_LAUNCH("attention_scored (merge)");
@@ -462,17 +512,21 @@ __global__ void turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __re
 // the row's position (pairs (i, i + rot/2); cosine and sine times `mscale`); queries are written back in place, keys
 // go to their pages, values (n_v heads of dv) are stored as they are.  A block per row; the row's queries and keys
 // lie in shared memory as 32-bit numbers while their sums of squares are taken, a warp per span.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src, int64_t ld_v,
                        const void* __restrict__ wq, const void* __restrict__ wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k,
                        float eps, const float* __restrict__ freq, int rot, float mscale, const int* __restrict__ row_seq,
                        const int* __restrict__ row_pos, const int* __restrict__ page_table, int table_width, T* __restrict__ k_pages,
                        T* __restrict__ v_pages, int n_heads, int n_kv, int n_v, int dk, int dv) {
+  // VEC: rows are read and written in 16-byte pieces (head sizes, strides and addresses allow it); the arithmetic is the same
+  constexpr int E = VEC ? 16 / (int)sizeof(T) : 1;
   extern __shared__ float nts[];
   const int nq = n_heads * dk, nk = n_kv * dk, spans_q = span_q > 0 ? nq / span_q : 0, spans_k = span_k > 0 ? nk / span_k : 0;
   float* xs = nts;                      // [nq + nk] the row's queries, then its keys
   float* inv = nts + nq + nk;           // [spans_q + spans_k]
+  float* cs_t = inv + spans_q + spans_k;   // [rot / 2] cosines, then [rot / 2] sines: one per pair, shared by every head of the row
+  float* sn_t = cs_t + rot / 2;
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
@@ -480,7 +534,32 @@ norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_
   const int64_t page = page_table[(int64_t)row_seq[r] * table_width + pos / PAGE];
   T* qr = q + (int64_t)r * ld_q;
   const T* kr = k_src + (int64_t)r * ld_k;
-  for (int i = tid; i < nq + nk; i += blockDim.x) xs[i] = i < nq ? to_f32(qr[i]) : to_f32(kr[i - nq]);
+  const T* vr = v_src + (int64_t)r * ld_v;
+  for (int i = tid; i < (nq + nk) / E; i += blockDim.x) {
+    const int c = i * E;
+    const T* src = c < nq ? qr + c : kr + (c - nq);
+    if (VEC) {
+      float f[E];
+      unpack16(*reinterpret_cast<const uint4*>(src), f, T());
+#pragma unroll
+      for (int e = 0; e < E; ++e) xs[c + e] = f[e];
+    } else {
+      xs[c] = to_f32(*src);
+    }
+  }
+  // (the values do not change: straight to their page, while the queries and keys are worked on)
+  for (int i = tid; i < n_v * dv / E; i += blockDim.x) {
+    const int c = i * E, h = c / dv, d = c - h * dv;
+    T* dst = v_pages + ((page * n_v + h) * PAGE + pos % PAGE) * dv + d;
+    if (VEC) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vr + c);
+    else *dst = vr[c];
+  }
+  for (int p = tid; p < rot / 2; p += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * freq[p], &sn, &cs);
+    cs_t[p] = cs * mscale;
+    sn_t[p] = sn * mscale;
+  }
   __syncthreads();
   for (int sp = warp; sp < spans_q + spans_k; sp += n_warps) {
     const bool is_q = sp < spans_q;
@@ -494,39 +573,47 @@ norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_
   __syncthreads();
   const int half = rot / 2, per_head = half + (dk - rot);         // units of a head: pairs that turn, entries that pass
   const int units = (n_heads + n_kv) * per_head;
-  for (int i = tid; i < units; i += blockDim.x) {
+  for (int i = tid; i < units; i += blockDim.x) {                  // (in place in shared memory: the units do not overlap)
     const int hd = i / per_head, p = i - hd * per_head;
     const bool is_q = hd < n_heads;
     const int col0 = hd * dk;                                      // the head's first column among [queries | keys]
     const int own0 = is_q ? col0 : col0 - nq;                      // ... within its own projection
     const void* w = is_q ? wq : wk;
     const int wlen = is_q ? wlen_q : wlen_k, span = is_q ? span_q : span_k;
-    T* dst = is_q ? qr + own0 : k_pages + ((page * n_kv + (hd - n_heads)) * PAGE + pos % PAGE) * dk;
+    const float f = span > 0 ? inv[(is_q ? 0 : spans_q) + own0 / span] : 1.f;      // (a head never straddles two spans)
     if (p < half) {
       const int ea = p, eb = p + half;
       float u = xs[col0 + ea], v = xs[col0 + eb];
       if (span > 0) {
-        const float f = inv[(is_q ? 0 : spans_q) + own0 / span];   // (a head never straddles two spans)
         u *= f * (w ? load_param(w, (own0 + ea) % wlen, w_f32) : 1.f);
         v *= f * (w ? load_param(w, (own0 + eb) % wlen, w_f32) : 1.f);
       }
-      float sn, cs;
-      sincosf((float)pos * freq[p], &sn, &cs);
-      sn *= mscale;
-      cs *= mscale;
-      dst[ea] = from_f32<T>(turn_first(u, v, cs, sn));
-      dst[eb] = from_f32<T>(turn_second(u, v, cs, sn));
+      const float cs = cs_t[p], sn = sn_t[p];
+      xs[col0 + ea] = turn_first(u, v, cs, sn);
+      xs[col0 + eb] = turn_second(u, v, cs, sn);
     } else {
       const int e = rot + (p - half);
-      float u = xs[col0 + e];
-      if (span > 0) u *= inv[(is_q ? 0 : spans_q) + own0 / span] * (w ? load_param(w, (own0 + e) % wlen, w_f32) : 1.f);
-      dst[e] = from_f32<T>(u);
+      if (span > 0) xs[col0 + e] *= f * (w ? load_param(w, (own0 + e) % wlen, w_f32) : 1.f);
     }
   }
-  const T* vr = v_src + (int64_t)r * ld_v;
-  for (int i = tid; i < n_v * dv; i += blockDim.x) {
-    const int h = i / dv, d = i - h * dv;
-    v_pages[((page * n_v + h) * PAGE + pos % PAGE) * dv + d] = vr[i];
+  __syncthreads();
+  for (int i = tid; i < (nq + nk) / E; i += blockDim.x) {
+    const int c = i * E;
+    T* dst;
+    if (c < nq) {
+      dst = qr + c;
+    } else {
+      const int ck = c - nq, h = ck / dk, d = ck - h * dk;
+      dst = k_pages + ((page * n_kv + h) * PAGE + pos % PAGE) * dk + d;
+    }
+    if (VEC) {
+      T y[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) y[e] = from_f32<T>(xs[c + e]);
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(y);
+    } else {
+      *dst = from_f32<T>(xs[c]);
+    }
   }
 }
 
@@ -675,7 +762,7 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
                                       int table_width, const void* k_pages, const void* v_pages, int n_seqs, int n_heads,
                                       int n_kv_heads, int dk, int dv, int page_size, int max_new, int hp, float scale,
                                       float softcap, float slope_span, int window, int keep_first, int n_splits, float* partial,
-                                      int key_maps, int out_f32, cudaStream_t stream) {
+                                      int key_maps, int out_f32, int merge, cudaStream_t stream) {
   KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && table_width > 0 && max_new >= 0,
                "attention (scored): bad sizes seqs=%d heads=%d kv_heads=%d dk=%d dv=%d", n_seqs, n_heads, n_kv_heads, dk, dv);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
@@ -698,7 +785,7 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   a.ld_k = dk; a.k_head_stride = (int64_t)PAGE * dk; a.k_page_stride = (int64_t)n_kv_heads * PAGE * dk;
   a.ld_v = alias ? dk : dv; a.v_head_stride = (int64_t)PAGE * a.ld_v; a.v_page_stride = (int64_t)(n_kv_heads / key_maps) * PAGE * a.ld_v;
   a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.dk = dk; a.dv = dv; a.hp = hp; a.v_alias = alias ? 1 : 0;
-  a.n_splits = n_splits; a.partial = partial; a.key_maps = key_maps; a.out_f32 = out_f32 ? 1 : 0;
+  a.n_splits = n_splits; a.partial = partial; a.key_maps = key_maps; a.out_f32 = out_f32 ? 1 : 0; a.merge = merge ? 1 : 0;
   const int piece = dtype == KVAD_DTYPE_F32 ? 4 : 8;
   a.vec_k = (dk % piece == 0 && (reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) ? 1 : 0;
   a.vec_v = (!alias && dv % piece == 0 && (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0) ? 1 : 0;
@@ -798,25 +885,55 @@ KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const voi
   KVAD_REQUIRE(q && k_src && v_src && k_pages && v_pages, "norm_turn_store: bad arguments");
   if (n_rows == 0) return KVAD_OK;
   const int nq = n_heads * dk, nk = n_kv * dk;
-  const size_t smem = ((size_t)nq + nk + (span_q ? nq / span_q : 0) + (span_k ? nk / span_k : 0)) * sizeof(float);
+  const size_t smem = ((size_t)nq + nk + (span_q ? nq / span_q : 0) + (span_k ? nk / span_k : 0) + rot) * sizeof(float);
   KVAD_REQUIRE(smem <= 200 * 1024, "norm_turn_store: rows of %d queries and keys do not fit shared memory", nq + nk);
+  const int threads = nq + nk >= 2048 ? 256 : 128;      // (short rows: smaller blocks, more rows an SM)
 #define KVAD_NTS(T)                                                                                                                          \
   do {                                                                                                                                       \
     static size_t configured = 0;                                                                                                            \
     if (smem > 48 * 1024 && smem > configured) {                                                                                             \
-      cudaError_t e = cudaFuncSetAttribute(norm_turn_store_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
+      cudaError_t e = cudaFuncSetAttribute(norm_turn_store_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(norm_turn_store_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "norm_turn_store: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
       configured = smem;                                                                                                                     \
     }                                                                                                                                        \
-    kvad_launch(norm_turn_store_kernel<T>, dim3(n_rows), dim3(256), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, wq, wk, \
-                w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width, (T*)k_pages,       \
-                (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                                    \
+    const int piece = 16 / (int)sizeof(T);                                                                                                   \
+    const bool vec = dk % piece == 0 && dv % piece == 0 && ld_q % piece == 0 && ld_k % piece == 0 && ld_v % piece == 0 &&                    \
+                     ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_src) | reinterpret_cast<uintptr_t>(v_src) |            \
+                       reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0;                              \
+    if (vec)                                                                                                                                 \
+      kvad_launch(norm_turn_store_kernel<T, true>, dim3(n_rows), dim3(threads), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, \
+                  wq, wk, w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
+                  (T*)k_pages, (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                     \
+    else                                                                                                                                     \
+      kvad_launch(norm_turn_store_kernel<T, false>, dim3(n_rows), dim3(threads), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, \
+                  wq, wk, w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
+                  (T*)k_pages, (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                     \
   } while (0)
   if (dtype == KVAD_DTYPE_F32) KVAD_NTS(float);
   else if (dtype == KVAD_DTYPE_BF16) KVAD_NTS(__nv_bfloat16);
   else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "norm_turn_store: unknown dtype %d", dtype);
 #undef KVAD_NTS
   KVAD_CHECK_LAUNCH("norm_turn_store");
+  return KVAD_OK;
+}
+
+// partial: what kvad_attention_scored left with `merge` 0 for 2 x n_heads query heads ([kv head][map][head of the group]) of
+// single-token rows; out: [rows, n_heads x dv] of `dtype`.
+KVAD_EXPORT int kvad_scored_merge_diff(int dtype, const float* partial, int n_splits, int n_rows, int n_heads, int group, int dv, void* out,
+                                       int64_t ld_out, float lambda, float eps, float gain, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_splits >= 1 && n_heads > 0 && group > 0 && n_heads % group == 0 && dv > 0 && dv <= 512 && partial && out,
+               "scored_merge_diff: bad arguments");
+  KVAD_REQUIRE(n_rows <= 2147483647 && n_heads <= 65535, "scored_merge_diff: too many heads for one launch");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(n_rows, n_heads), block(128);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(scored_merge_diff_kernel<float>, grid, block, 0, stream, partial, n_splits, n_heads, group, dv, (float*)out, ld_out, lambda, eps, gain);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(scored_merge_diff_kernel<__nv_bfloat16>, grid, block, 0, stream, partial, n_splits, n_heads, group, dv, (__nv_bfloat16*)out, ld_out,
+                lambda, eps, gain);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "scored_merge_diff: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("scored_merge_diff");
   return KVAD_OK;
 }
 

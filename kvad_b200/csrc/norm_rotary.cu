@@ -270,6 +270,23 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// The same for widths and strides in fours: a thread takes four neighbouring columns (one 16-byte load).
+template <typename TO>
+__global__ void cast_rows_vec_kernel(const float* __restrict__ x, const int* __restrict__ row_index, TO* __restrict__ out, int64_t ld_out,
+                                     int n_rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = width / 4;
+  const int64_t total = (int64_t)n_rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = (int)(i - r * per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + (int64_t)(row_index ? row_index[r] : r) * width + c);
+    TO* o = out + r * ld_out + c;
+    o[0] = from_f32<TO>(v.x); o[1] = from_f32<TO>(v.y); o[2] = from_f32<TO>(v.z); o[3] = from_f32<TO>(v.w);
+  }
+}
+
 // delta += mult * (ga * a / rms(a) + gb * b / rms(b)); a = 0; b = 0 (all 32-bit, rows of `width`; ga, gb one number per
 // column).  A block per row; the two sums of squares run in column order through the same tree.
 __global__ void __launch_bounds__(128)
@@ -485,6 +502,13 @@ KVAD_EXPORT int kvad_cast_rows(int out_dtype, const float* x, const int* row_ind
   KVAD_REQUIRE(n_rows >= 0 && width > 0 && x && out && ld_out >= width, "cast_rows: bad arguments");
   if (n_rows == 0) return KVAD_OK;
   dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (width % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (out_dtype == KVAD_DTYPE_F32 || out_dtype == KVAD_DTYPE_BF16)) {
+    dim3 grid4(flat_blocks((int64_t)n_rows * (width / 4), 256));
+    if (out_dtype == KVAD_DTYPE_F32) kvad_launch(cast_rows_vec_kernel<float>, grid4, block, 0, stream, x, row_index, (float*)out, ld_out, n_rows, width);
+    else kvad_launch(cast_rows_vec_kernel<__nv_bfloat16>, grid4, block, 0, stream, x, row_index, (__nv_bfloat16*)out, ld_out, n_rows, width);
+    KVAD_CHECK_LAUNCH("cast_rows");
+    return KVAD_OK;
+  }
   if (out_dtype == KVAD_DTYPE_F32) kvad_launch(cast_rows_kernel<float>, grid, block, 0, stream, x, row_index, (float*)out, ld_out, n_rows, width);
   else if (out_dtype == KVAD_DTYPE_BF16)
     kvad_launch(cast_rows_kernel<__nv_bfloat16>, grid, block, 0, stream, x, row_index, (__nv_bfloat16*)out, ld_out, n_rows, width);

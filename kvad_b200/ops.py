@@ -102,7 +102,8 @@ _SIGNATURES = {
     "attention_scored": {
         "kvad_attention_scored": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "kvad_scored_merge_diff": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_float, c_float, c_float, c_void_p],
         "kvad_norm_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -919,6 +920,20 @@ class Ops:
                                       float(mscale), _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(k_pages),
                                       _ptr(v_pages), n, int(n_heads), n_kv, n_v, dk, dv, page, _stream()), h)
 
+    def scored_merge_diff(self, scratch, n_splits: int, out, n_heads: int, group: int, lam: float, eps: float, gain: float) -> None:
+        """The merge of `attention_scored`'s parts (left with `merge=False`, 2 x `n_heads` query heads of single-token rows laid out
+        [kv head][map][head of the group]) and `diff_combine` in one launch: out[r, h] = gain * o / sqrt(mean(o^2) + eps),
+        o = a1 - lam * a2."""
+        _need_cuda(scratch, out)
+        n, total = out.shape
+        dv = total // n_heads
+        if (scratch.dtype != torch.float32 or out.dtype != self.dtype or dv * n_heads != total or n_heads % group
+                or scratch.numel() < n * 2 * n_heads * n_splits * (dv + 2)):
+            raise KernelError(f"scored_merge_diff: float32 parts of rows x 2 heads x splits x (value size + 2) and an output [rows, heads x dv] of {self.dtype}")
+        h = lib("attention_scored")
+        _check(h.kvad_scored_merge_diff(self.code, _ptr(scratch), int(n_splits), n, int(n_heads), int(group), dv, _ptr(out),
+                                        _rows_view(out, "scored_merge_diff output"), float(lam), float(eps), float(gain), _stream()), h)
+
     def diff_combine(self, maps, out, n_heads: int, group: int, lam: float, eps: float, gain: float) -> None:
         """out[r, h] = gain * o / sqrt(mean(o^2) + eps), o = a1 - lam * a2 over a head's values, where `maps` (float32
         [rows, 2 heads x dv]) holds the two maps' outputs as [kv head][map][head of the group][dv] and h = kv head x group + head
@@ -974,7 +989,7 @@ class Ops:
     def attention_scored(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages, n_heads: int,
                          scale: float, *, value_dim: Optional[int] = None, softcap: float = 0.0, slope_span: float = 0.0,
                          window: int = 0, keep_first: int = 0, gate=None, heads_per_block: int = 1, n_splits: int = 1,
-                         scratch=None, key_maps: int = 1) -> None:
+                         scratch=None, key_maps: int = 1, merge: bool = True) -> None:
         """Softmax attention of packed rows (each sequence's rows are its last positions) over the paged cache with
         shaped scores: s = q.k * scale, capped by `softcap` * tanh(s / softcap) if positive, less slope_h * distance with
         slope_h = 2^(-slope_span (h+1) / n_heads) if `slope_span` is positive; a row sees the last `window` positions
@@ -982,7 +997,8 @@ class Ops:
         keys.  `gate`: the output is multiplied by sigmoid(gate).  `n_splits` > 1 (single-token rows): the keys of a
         row and head are dealt out to that many blocks and merged by a second kernel through `scratch` (float32, rows x
         heads x n_splits x (value size + 2)).  `key_maps` > 1: that many consecutive key heads read one value head (the values'
-        pages have kv heads / key_maps heads).  `out` may be float32 whatever the compute dtype (no gate then).  32-bit
+        pages have kv heads / key_maps heads).  `out` may be float32 whatever the compute dtype (no gate then).  `merge` False (with
+        `n_splits` > 1): the parts stay in `scratch` for a merge of the caller's (`scored_merge_diff`), `out` is not written.  32-bit
         arithmetic on the CUDA cores."""
         _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages, gate)
         ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
@@ -1014,8 +1030,8 @@ class Ops:
                                        _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_ptr), int(n_seqs), int(n_heads), n_kv,
                                        dk, dv, page, int(max_new), int(heads_per_block), float(scale), float(softcap or 0.0),
                                        float(slope_span or 0.0), int(window or 0), int(keep_first or 0), int(n_splits),
-                                       _ptr(scratch if n_splits > 1 else None), int(key_maps), int(out_f32), _stream()), h)
-        if n_splits > 1:
+                                       _ptr(scratch if n_splits > 1 else None), int(key_maps), int(out_f32), int(bool(merge)), _stream()), h)
+        if n_splits > 1 and merge:
             global _launches
             _launches += 1          # the merge kernel
 

@@ -372,18 +372,21 @@ class DifferentialAttention(Mixer):
                             q_weight=self.q_norm, k_weight=self.k_norm, span_q=self.key_dim if self.normed else 0,
                             span_k=self.key_dim if self.normed else 0, eps=self.eps, inv_freq=pos.inv_freq if pos is not None else None,
                             dims=pos.dims if pos is not None else 0, mscale=pos.mscale if pos is not None else 1.0)
-        maps = ctx.buffer((n, 2 * self.o_width), torch.float32)
         splits, scratch = 1, None
         if b.is_decode:
             reach = self.window if self.window else view.page_table.shape[1] * view.page_size
             splits = ops.scored_splits(n, 2 * self.n_kv_heads, self.group, reach)
             scratch = ctx.buffer((n * 2 * self.n_heads * splits * (self.value_dim + 2),), torch.float32) if splits > 1 else None
+        mixed = ctx.buffer((n, self.o_width))
+        maps = ctx.buffer((n, 2 * self.o_width), torch.float32)
         ops.attention_scored(q, maps, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages, view.v_pages,
                              2 * self.n_heads, self.score_scale, window=self.window or 0,
                              heads_per_block=min(self.group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch,
-                             key_maps=2)
-        mixed = ctx.buffer((n, self.o_width))
-        ops.diff_combine(maps, mixed, self.n_heads, self.group, self.lam, self.eps, 1.0 - self.diff)
+                             key_maps=2, merge=False)
+        if splits > 1:      # the keys' parts are merged, the second map taken off the first and the head made a unit vector in one launch
+            ops.scored_merge_diff(scratch, splits, mixed, self.n_heads, self.group, self.lam, self.eps, 1.0 - self.diff)
+        else:
+            ops.diff_combine(maps, mixed, self.n_heads, self.group, self.lam, self.eps, 1.0 - self.diff)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

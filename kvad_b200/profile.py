@@ -27,7 +27,8 @@ _TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0
           "rmsnorm": 3, "scale_add": 0, "rotary": 0, "gate_mul": 2, "kv_store_blend": 0, "latent_store": 0, "attention_scored": 0, "retention": 0, "linear_heads": 0,
           "gated_recurrence": 1, "short_conv": 0, "conv_state": 0, "head_norm_gate": 0, "moe_route": 0, "moe_sort": 0, "grouped_linear": 0,
           "clamped_glu": 2, "moe_combine": 0, "decay_gate": 0, "gather_rows": 2,
-          "postnorm_rmsnorm": 0, "head_gate": 0, "stream_concat": 0, "turn_store": 0, "relu_squared": 0, "residual_conv": 0, "conv_keep": 0, "min_gru": 0}
+          "postnorm_rmsnorm": 0, "head_gate": 0, "stream_concat": 0, "turn_store": 0, "relu_squared": 0, "residual_conv": 0, "conv_keep": 0, "min_gru": 0,
+          "cast_rows": 1, "pair_norm_sum": 0, "tanh_cap": 0, "norm_turn_store": 0, "diff_combine": 0, "scored_merge_diff": 2, "row_norm_gate": 0, "scaled_glu": 2}
 
 _records: list = []       # (label, start event, end event, held)
 _registered = False

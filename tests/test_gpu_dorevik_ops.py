@@ -151,7 +151,7 @@ def test_two_maps_over_the_same_values_prompts_portions_and_single_rows(dtype, H
                        window, lam, eps, gain).reshape(n, -1) for n, (q, k, v) in zip(lens, data)]
     group = H // G
 
-    def step(spans, single):
+    def step(spans, single, fused=False):
         live = [s for s, (_, r) in enumerate(spans) if r]
         q = dev(np.concatenate([to_map_groups(data[s][0][a:a + r].reshape(r, H, 2, dk), H, G, dk) for s, (a, r) in enumerate(spans) if r]), DT[dtype])
         k, v = (dev(np.concatenate([data[s][i][a:a + r] for s, (a, r) in enumerate(spans) if r]), DT[dtype]) for i in (1, 2))
@@ -165,9 +165,12 @@ def test_two_maps_over_the_same_values_prompts_portions_and_single_rows(dtype, H
         scratch = nan_like((len(seq) * 2 * H * splits * (dv + 2),), torch.float32) if single else None
         ops.attention_scored(q, maps, starts, dev([sum(spans[s]) for s in live], torch.int32), len(live), max(r for _, r in spans), table,
                              cache.k_pages, cache.v_pages, 2 * H, scale, window=window, key_maps=2, n_splits=splits, scratch=scratch,
-                             heads_per_block=min(group, 32) if single else max(d for d in (1, 2, 4) if group % d == 0))
+                             heads_per_block=min(group, 32) if single else max(d for d in (1, 2, 4) if group % d == 0), merge=not fused)
         out = nan_like((len(seq), H * dv), DT[dtype])
-        ops.diff_combine(maps, out, H, group, lam, eps, gain)
+        if fused:      # the parts' merge and the maps' difference in one launch
+            ops.scored_merge_diff(scratch, splits, out, H, group, lam, eps, gain)
+        else:
+            ops.diff_combine(maps, out, H, group, lam, eps, gain)
         o, at, res = out.double().cpu().numpy(), 0, {}
         for s in live:
             res[s] = o[at:at + spans[s][1]]
@@ -187,7 +190,7 @@ def test_two_maps_over_the_same_values_prompts_portions_and_single_rows(dtype, H
             a, r = cuts[s][j]
             assert rel(torch.as_tensor(got[s]), want[s][a:a + r]) < tol, ("portion", j, s)
     for p in range(125, 150):
-        got = step([(p, 1), (0, 0), (0, 0)], True)
+        got = step([(p, 1), (0, 0), (0, 0)], True, fused=p % 2 == 0)
         assert rel(torch.as_tensor(got[0]), want[0][p:p + 1]) < tol, ("single", p)
 
 
