@@ -561,58 +561,48 @@ norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_
     sn_t[p] = sn * mscale;
   }
   __syncthreads();
-  for (int sp = warp; sp < spans_q + spans_k; sp += n_warps) {
-    const bool is_q = sp < spans_q;
-    const int len = is_q ? span_q : span_k;
-    const float* x = is_q ? xs + sp * span_q : xs + nq + (sp - spans_q) * span_k;
-    float sq = 0.f;
-    for (int c = lane; c < len; c += 32) sq = fmaf(x[c], x[c], sq);
-    sq = warp_sum(sq);
-    if (lane == 0) inv[sp] = 1.0f / sqrtf(sq / (float)len + eps);
+  const int half = rot / 2;
+  const int hps_q = span_q > 0 ? span_q / dk : 1, hps_k = span_k > 0 ? span_k / dk : 1;       // heads that are normed together
+  const bool by_head = hps_q == 1 && hps_k == 1;
+  if (!by_head) {                                                  // several heads are normed together: their sums first, a warp per span
+    for (int sp = warp; sp < spans_q + spans_k; sp += n_warps) {
+      const bool is_q = sp < spans_q;
+      const int len = is_q ? span_q : span_k;
+      const float* x = is_q ? xs + sp * span_q : xs + nq + (sp - spans_q) * span_k;
+      float sq = 0.f;
+      for (int c = lane; c < len; c += 32) sq = fmaf(x[c], x[c], sq);
+      sq = warp_sum(sq);
+      if (lane == 0) inv[sp] = 1.0f / sqrtf(sq / (float)len + eps);
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  const int half = rot / 2, per_head = half + (dk - rot);         // units of a head: pairs that turn, entries that pass
-  const int units = (n_heads + n_kv) * per_head;
-  for (int i = tid; i < units; i += blockDim.x) {                  // (in place in shared memory: the units do not overlap)
-    const int hd = i / per_head, p = i - hd * per_head;
+  // A warp takes a head at a time, a lane an entry at a time: the entry is normed (a weight is as long as what is normed
+  // together, so a head's entries find theirs at the head's place within its span), turned with its partner half the turned
+  // entries away (read from shared memory, which nothing writes any more), and goes straight to the queries' row or the key's page.
+  for (int hd = warp; hd < n_heads + n_kv; hd += n_warps) {
     const bool is_q = hd < n_heads;
-    const int col0 = hd * dk;                                      // the head's first column among [queries | keys]
-    const int own0 = is_q ? col0 : col0 - nq;                      // ... within its own projection
-    const void* w = is_q ? wq : wk;
-    const int wlen = is_q ? wlen_q : wlen_k, span = is_q ? span_q : span_k;
-    const float f = span > 0 ? inv[(is_q ? 0 : spans_q) + own0 / span] : 1.f;      // (a head never straddles two spans)
-    if (p < half) {
-      const int ea = p, eb = p + half;
-      float u = xs[col0 + ea], v = xs[col0 + eb];
-      if (span > 0) {
-        u *= f * (w ? load_param(w, (own0 + ea) % wlen, w_f32) : 1.f);
-        v *= f * (w ? load_param(w, (own0 + eb) % wlen, w_f32) : 1.f);
+    const int hl = is_q ? hd : hd - n_heads, span = is_q ? span_q : span_k, hps = is_q ? hps_q : hps_k;
+    const float* x = xs + hd * dk;
+    const int sp = hl / hps;
+    float f = 1.f;
+    if (span > 0 && by_head) {
+      float sq = 0.f;
+      for (int e = lane; e < dk; e += 32) sq = fmaf(x[e], x[e], sq);
+      f = 1.0f / sqrtf(warp_sum(sq) / (float)dk + eps);
+    } else if (span > 0) {
+      f = inv[(is_q ? 0 : spans_q) + sp];
+    }
+    const void* w = span > 0 ? (is_q ? wq : wk) : nullptr;
+    const int wbase = (hl - sp * hps) * dk;
+    T* dst = is_q ? qr + hl * dk : k_pages + ((page * n_kv + hl) * PAGE + pos % PAGE) * dk;
+    for (int e = lane; e < dk; e += 32) {
+      float y = x[e] * f * (w ? load_param(w, wbase + e, w_f32) : 1.f);
+      if (e < rot) {
+        const int pe = e < half ? e + half : e - half, pr = e < half ? e : e - half;
+        const float z = x[pe] * f * (w ? load_param(w, wbase + pe, w_f32) : 1.f);
+        y = e < half ? turn_first(y, z, cs_t[pr], sn_t[pr]) : turn_second(z, y, cs_t[pr], sn_t[pr]);
       }
-      const float cs = cs_t[p], sn = sn_t[p];
-      xs[col0 + ea] = turn_first(u, v, cs, sn);
-      xs[col0 + eb] = turn_second(u, v, cs, sn);
-    } else {
-      const int e = rot + (p - half);
-      if (span > 0) xs[col0 + e] *= f * (w ? load_param(w, (own0 + e) % wlen, w_f32) : 1.f);
-    }
-  }
-  __syncthreads();
-  for (int i = tid; i < (nq + nk) / E; i += blockDim.x) {
-    const int c = i * E;
-    T* dst;
-    if (c < nq) {
-      dst = qr + c;
-    } else {
-      const int ck = c - nq, h = ck / dk, d = ck - h * dk;
-      dst = k_pages + ((page * n_kv + h) * PAGE + pos % PAGE) * dk + d;
-    }
-    if (VEC) {
-      T y[E];
-#pragma unroll
-      for (int e = 0; e < E; ++e) y[e] = from_f32<T>(xs[c + e]);
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(y);
-    } else {
-      *dst = from_f32<T>(xs[c]);
+      dst[e] = from_f32<T>(y);
     }
   }
 }
