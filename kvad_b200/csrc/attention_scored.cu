@@ -513,7 +513,7 @@ __global__ void turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __re
 // go to their pages, values (n_v heads of dv) are stored as they are.  A block per row; the row's queries and keys
 // lie in shared memory as 32-bit numbers while their sums of squares are taken, a warp per span.
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src, int64_t ld_v,
                        const void* __restrict__ wq, const void* __restrict__ wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k,
                        float eps, const float* __restrict__ freq, int rot, float mscale, const int* __restrict__ row_seq,
@@ -877,7 +877,9 @@ KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const voi
   const int nq = n_heads * dk, nk = n_kv * dk;
   const size_t smem = ((size_t)nq + nk + (span_q ? nq / span_q : 0) + (span_k ? nk / span_k : 0) + rot) * sizeof(float);
   KVAD_REQUIRE(smem <= 200 * 1024, "norm_turn_store: rows of %d queries and keys do not fit shared memory", nq + nk);
-  const int threads = nq + nk >= 2048 ? 256 : 128;      // (short rows: smaller blocks, more rows an SM)
+  // many rows: short rows take smaller blocks, more rows an SM; few rows (single tokens): a warp per head, so that no warp walks several
+  const int per_head = 32 * (n_heads + n_kv);
+  const int threads = n_rows <= 2 * 148 ? (per_head > 1024 ? 1024 : (per_head < 128 ? 128 : per_head)) : (nq + nk >= 2048 ? 256 : 128);
 #define KVAD_NTS(T)                                                                                                                          \
   do {                                                                                                                                       \
     static size_t configured = 0;                                                                                                            \

@@ -158,7 +158,7 @@ def _mixer_spec(c: DorevikConfig, layer: dict) -> PartSpec:
     left = PartSpec("shaped_score_attention", {
         "width": c.width, "n_heads": l["heads"], "n_kv_heads": l.get("kv_heads") or l["heads"], "key_dim": l["dim"], "value_dim": l["vdim"],
         "score_scale": l["scale"], "window": l["mask"]["size"], "position": _rotary(l["rot"]),
-        "qk_norm": {"span": "all", "eps": c.norm_eps, "q_name": "q.norm", "k_name": "k.norm"}})
+        "qk_norm": {"span": "all", "eps": c.norm_eps, "q_name": "q.norm", "k_name": "k.norm"}, "decode_blocks_per_sm": 4})
     right = PartSpec("retention", {
         "width": c.width, "n_heads": r["heads"], "key_dim": r["dim"], "value_dim": r["vdim"], "decay": tuple(r["decay"]),
         "activation": "silu", "row_norm": {"name": "norm", "eps": c.norm_eps}, "gate": True})

@@ -1036,12 +1036,12 @@ class Ops:
             _launches += 1          # the merge kernel
 
     @staticmethod
-    def scored_splits(n_rows: int, n_kv_heads: int, group: int, reach: int, n_sms: Optional[int] = None) -> int:
+    def scored_splits(n_rows: int, n_kv_heads: int, group: int, reach: int, n_sms: Optional[int] = None, per_sm: int = 2) -> int:
         """Into how many parts single-token rows cut the keys of a (row, key/value head): enough blocks for two
-        an SM, one part per 64 keys of `reach` (the window plus the kept first positions, or the longest sequence the
+        an SM (`per_sm`), one part per 64 keys of `reach` (the window plus the kept first positions, or the longest sequence the
         cache holds) at most, 16 at most.  Depends on the batch's size and the layer's constants only."""
         blocks = max(1, n_rows * n_kv_heads * -(-group // 32))
-        want = (2 * (n_sms or sm_count())) // blocks
+        want = (int(per_sm) * (n_sms or sm_count())) // blocks
         return max(1, min(want, -(-reach // 64) + 1, 16))
 
     # -- retention ------------------------------------------------------------------------
