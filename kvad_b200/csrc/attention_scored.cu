@@ -564,6 +564,7 @@ norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_
   const int half = rot / 2;
   const int hps_q = span_q > 0 ? span_q / dk : 1, hps_k = span_k > 0 ? span_k / dk : 1;       // heads that are normed together
   const bool by_head = hps_q == 1 && hps_k == 1;
+  const float inv_dk = 1.0f / (float)dk;
   if (!by_head) {                                                  // several heads are normed together: their sums first, a warp per span
     for (int sp = warp; sp < spans_q + spans_k; sp += n_warps) {
       const bool is_q = sp < spans_q;
@@ -583,12 +584,12 @@ norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_
     const bool is_q = hd < n_heads;
     const int hl = is_q ? hd : hd - n_heads, span = is_q ? span_q : span_k, hps = is_q ? hps_q : hps_k;
     const float* x = xs + hd * dk;
-    const int sp = hl / hps;
+    const int sp = hps == 1 ? hl : hl / hps;
     float f = 1.f;
     if (span > 0 && by_head) {
       float sq = 0.f;
       for (int e = lane; e < dk; e += 32) sq = fmaf(x[e], x[e], sq);
-      f = 1.0f / sqrtf(warp_sum(sq) / (float)dk + eps);
+      f = rsqrtf(fmaf(warp_sum(sq), inv_dk, eps));
     } else if (span > 0) {
       f = inv[(is_q ? 0 : spans_q) + sp];
     }
