@@ -508,14 +508,14 @@ __global__ void turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __re
 }
 
 // Queries and keys RMS-normed in 32-bit (over `span` consecutive entries of their row at a time: one head, or the whole
-// projection; weight entry (column % w_len), absent weights are ones), then the first `rot` entries of every head turned by
+// projection; a weight is as long as a span, absent weights are ones), then the first `rot` entries of every head turned by
 // the row's position (pairs (i, i + rot/2); cosine and sine times `mscale`); queries are written back in place, keys
 // go to their pages, values (n_v heads of dv) are stored as they are.  A block per row; the row's queries and keys
 // lie in shared memory as 32-bit numbers while their sums of squares are taken, a warp per span.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(1024)
 norm_turn_store_kernel(T* __restrict__ q, int64_t ld_q, const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src, int64_t ld_v,
-                       const void* __restrict__ wq, const void* __restrict__ wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k,
+                       const void* __restrict__ wq, const void* __restrict__ wk, int w_f32, int span_q, int span_k,
                        float eps, const float* __restrict__ freq, int rot, float mscale, const int* __restrict__ row_seq,
                        const int* __restrict__ row_pos, const int* __restrict__ page_table, int table_width, T* __restrict__ k_pages,
                        T* __restrict__ v_pages, int n_heads, int n_kv, int n_v, int dk, int dv) {
@@ -859,10 +859,10 @@ KVAD_EXPORT int kvad_latent_store(int dtype, const void* src, int64_t ld, const 
 }
 
 // span_q / span_k: how many consecutive entries of the queries' / keys' projection are normed together (0: no norm; a
-// multiple of dk that divides the projection); wq / wk: the norms' weights (w_len entries each, float32 or bfloat16; null:
-// ones).  n_v: value heads (the pages of values have that many).  rot: entries of a head that turn (even, at most dk).
+// multiple of dk that divides the projection); wq / wk: the norms' weights (as long as what is normed together, float32 or
+// bfloat16; null: ones).  n_v: value heads (the pages of values have that many).  rot: entries of a head that turn (even, at most dk).
 KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const void* k_src, int64_t ld_k, const void* v_src, int64_t ld_v,
-                                     const void* wq, const void* wk, int w_f32, int span_q, int span_k, int wlen_q, int wlen_k, float eps,
+                                     const void* wq, const void* wk, int w_f32, int span_q, int span_k, float eps,
                                      const float* freq, int rot, float mscale, const int* row_seq, const int* row_pos, const int* page_table,
                                      int table_width, void* k_pages, void* v_pages, int n_rows, int n_heads, int n_kv, int n_v, int dk, int dv,
                                      int page_size, cudaStream_t stream) {
@@ -872,7 +872,7 @@ KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const voi
   KVAD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "norm_turn_store: %d of %d key entries cannot turn in pairs", rot, dk);
   KVAD_REQUIRE(span_q >= 0 && span_k >= 0 && (span_q == 0 || (span_q % dk == 0 && (n_heads * dk) % span_q == 0)) &&
                (span_k == 0 || (span_k % dk == 0 && (n_kv * dk) % span_k == 0)), "norm_turn_store: norms over %d and %d entries do not fit heads of %d", span_q, span_k, dk);
-  KVAD_REQUIRE((wq == nullptr || wlen_q > 0) && (wk == nullptr || wlen_k > 0), "norm_turn_store: a weight needs its length");
+  KVAD_REQUIRE((wq == nullptr || span_q > 0) && (wk == nullptr || span_k > 0), "norm_turn_store: a weight goes with a norm");
   KVAD_REQUIRE(q && k_src && v_src && k_pages && v_pages, "norm_turn_store: bad arguments");
   if (n_rows == 0) return KVAD_OK;
   const int nq = n_heads * dk, nk = n_kv * dk;
@@ -896,11 +896,11 @@ KVAD_EXPORT int kvad_norm_turn_store(int dtype, void* q, int64_t ld_q, const voi
                        reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0;                              \
     if (vec)                                                                                                                                 \
       kvad_launch(norm_turn_store_kernel<T, true>, dim3(n_rows), dim3(threads), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, \
-                  wq, wk, w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
+                  wq, wk, w_f32, span_q, span_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
                   (T*)k_pages, (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                     \
     else                                                                                                                                     \
       kvad_launch(norm_turn_store_kernel<T, false>, dim3(n_rows), dim3(threads), smem, stream, (T*)q, ld_q, (const T*)k_src, ld_k, (const T*)v_src, ld_v, \
-                  wq, wk, w_f32, span_q, span_k, wlen_q, wlen_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
+                  wq, wk, w_f32, span_q, span_k, eps, freq, rot, mscale, row_seq, row_pos, page_table, table_width,          \
                   (T*)k_pages, (T*)v_pages, n_heads, n_kv, n_v, dk, dv);                                                                     \
   } while (0)
   if (dtype == KVAD_DTYPE_F32) KVAD_NTS(float);

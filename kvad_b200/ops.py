@@ -104,8 +104,8 @@ _SIGNATURES = {
                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_float, c_float, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "kvad_scored_merge_diff": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_float, c_float, c_float, c_void_p],
-        "kvad_norm_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                 c_int, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+        "kvad_norm_turn_store": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
+                                 c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_diff_combine": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
         "kvad_kv_store_blend": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
@@ -916,7 +916,7 @@ class Ops:
             raise KernelError("norm_turn_store: int32 sequences and positions, one per row")
         h = lib("attention_scored")
         _check(h.kvad_norm_turn_store(self.code, _ptr(q), ld_q, _ptr(k_src), ld_k, _ptr(v_src), ld_v, _ptr(q_weight), _ptr(k_weight), w_f32,
-                                      int(span_q), int(span_k), int(span_q), int(span_k), float(eps), _ptr(inv_freq if dims else None), int(dims),
+                                      int(span_q), int(span_k), float(eps), _ptr(inv_freq if dims else None), int(dims),
                                       float(mscale), _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(k_pages),
                                       _ptr(v_pages), n, int(n_heads), n_kv, n_v, dk, dv, page, _stream()), h)
 

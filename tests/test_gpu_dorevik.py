@@ -118,6 +118,36 @@ def test_whole_prompts_from_one_token_to_several_pages(engine, loaded, name, dty
     e.cache.book.check_all_free()
 
 
+@pytest.mark.parametrize("name", SMALL)
+def test_the_stream_after_every_layer(folders, loaded, name):
+    """Layer by layer in 32-bit: what every block leaves in the residual stream (the sum it still owes taken up), for a
+    prompt and for the token after it."""
+    from kvad_b200.parts.block import flush_deferred
+    e = Engine.from_pretrained(folders[name], "float32", max_tokens=512)
+    e.use_graphs = False
+    seen = []
+    for blk in e.model.blocks:
+        def wrap(inner):
+            def forward(ctx, x, call):
+                inner(ctx, x, call)
+                flush_deferred(ctx)
+                seen.append(x[:ctx.n_rows].cpu().numpy().copy())
+            return forward
+        blk.forward = wrap(blk.forward)
+    toks = random_tokens(5, 75, CONFIGS[name]["vocab"])
+    trace = {}
+    loaded[name].forward(toks, trace=trace)
+    s = e.open()
+    e.step([StepEntry(s, toks[:74], [73])])
+    e.step([StepEntry(s, toks[74:], [0])])
+    e.close(s)
+    n = len(CONFIGS[name]["layers"])
+    assert len(seen) == 2 * n
+    for i in range(n):
+        assert rel_err(seen[i], trace["streams"][i][:74]) < TOL["float32"], (name, "prompt", i)
+        assert rel_err(seen[n + i], trace["streams"][i][74:]) < TOL["float32"], (name, "token", i)
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_prompt_then_token_by_token_across_pages_and_windows(engine, loaded, name, dtype):
     """Every window of the small configurations (1 to 200 positions) is passed while single tokens are decoded, pages
