@@ -290,8 +290,8 @@ def dorevik_config(width, ff, vocab, heads, dim, window):
     together are as long as the other designs' keys) and the two mixers side by side (windowed attention beside linear attention with
     a decay, heads of 128 as in `nifulix_config`), dense and routed feed-forwards in turn (two chosen of eight experts plus a shared
     expert: together as wide as the dense `ff`, as in `vepinex_config`)."""
-    rot = {"base": 1e4, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
-    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5, "diff": 0.3,
+    rot = {"base": 1e4, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5, "diff": 0.25,
                                           "mask": {"size": window}, "rot": rot}}
     par = {"type": "parallel", "mixer": {
         "left": {"heads": heads // 2, "kv_heads": heads // 8, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},

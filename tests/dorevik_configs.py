@@ -72,7 +72,7 @@ CONFIGS = {
     # in bfloat16), windows that several pages pass through
     "D": model(256, 1000,
                [parallel((4, 2, 64, 64, 128, rot(32, 1e6)), (4, 64, 64, (0.7, 0.9, 0.97, 0.999))),
-                attention(4, 2, 64, 128, 100, rot(64, 2e4, (2.0, 256, 32.0, 1.0))),
+                attention(4, 2, 64, 128, 100, rot(64, 3e4, (2.0, 256, 24.0, 1.5))),
                 attention(8, 8, 32, 32, 513, rot(16, 1e5), diff=0.4),
                 parallel((2, 1, 128, 128, 70, rot(64, 1e4, (4.0, 128, 16.0, 1.0))), (2, 128, 128, (0.95, 0.995)))],
                [moe(16, 2, 64, shared=128), dense(512), moe(32, 4, 64), None], cap=20.0),

@@ -93,7 +93,7 @@ def test_configurations_that_are_refused_say_where(change, what):
 
 
 @pytest.mark.parametrize("rot", [
-    {"base": 2e4, "dims": 8, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}},
+    {"base": 3e4, "dims": 12, "scaling": {"factor": 6.0, "original": 512, "fast": 24.0, "slow": 2.0}},
     {"base": 1e4, "dims": 4, "scaling": {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}},
     {"base": 300.0, "dims": 12, "scaling": {"factor": 3.0, "original": 40, "fast": 10.0, "slow": 1.0}},
     {"base": 1e6, "dims": 64}])
